@@ -15,7 +15,7 @@ from typing import Any, Callable, Mapping
 from .config_json import ConfigError, read_config_json
 from .model_spec import ModelSpec
 
-SpecFactory = Callable[[Mapping[str, Any]], ModelSpec]
+SpecFactory = Callable[..., ModelSpec]
 
 
 @dataclass(frozen=True)
@@ -23,6 +23,9 @@ class ArchitectureEntry:
     name: str
     spec_from_config: SpecFactory
     model_types: tuple[str, ...] = ()
+    # an architecture some of whose sizes are only a tensor's shape: its factory then takes a second argument,
+    # the shapes of the folder's tensors by name (None when there is no folder)
+    reads_tensor_shapes: bool = False
 
 
 _ARCHITECTURES: dict[str, ArchitectureEntry] = {}
@@ -34,11 +37,13 @@ def register_architecture(
     *,
     model_types: tuple[str, ...] = (),
     replace: bool = False,
+    reads_tensor_shapes: bool = False,
 ) -> None:
-    """Add an architecture: ``spec_from_config(config_json_dict) -> ModelSpec``."""
+    """Add an architecture: ``spec_from_config(config_json_dict) -> ModelSpec``; with
+    ``reads_tensor_shapes`` the factory is called as ``spec_from_config(config_json_dict, shapes)``."""
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is already registered")
-    _ARCHITECTURES[name] = ArchitectureEntry(name, spec_from_config, tuple(model_types))
+    _ARCHITECTURES[name] = ArchitectureEntry(name, spec_from_config, tuple(model_types), bool(reads_tensor_shapes))
 
 
 def unregister_architecture(name: str) -> None:
@@ -67,12 +72,35 @@ def resolve_architecture(raw: Mapping[str, Any]) -> ArchitectureEntry:
     )
 
 
-def model_spec_from_config(raw: Mapping[str, Any]) -> ModelSpec:
-    return resolve_architecture(raw).spec_from_config(raw)
+def model_spec_from_config(raw: Mapping[str, Any],
+                           tensor_shapes: Mapping[str, tuple[int, ...]] | None = None) -> ModelSpec:
+    entry = resolve_architecture(raw)
+    if entry.reads_tensor_shapes:
+        return entry.spec_from_config(raw, tensor_shapes)
+    return entry.spec_from_config(raw)
+
+
+def folder_tensor_shapes(folder: str | Path) -> dict[str, tuple[int, ...]] | None:
+    """Name -> shape of every tensor in the folder's safetensors files (their headers only); None when the
+    folder holds no weights (a model that is filled with random numbers in place)."""
+    from ..weights.safetensors_io import SafetensorsFile, weight_files
+
+    try:
+        files = weight_files(folder)
+    except FileNotFoundError:
+        return None
+    shapes: dict[str, tuple[int, ...]] = {}
+    for path in files:
+        with SafetensorsFile(path) as handle:
+            shapes.update({name: entry.shape for name, entry in handle.entries.items()})
+    return shapes
 
 
 def model_spec_from_folder(folder: str | Path) -> ModelSpec:
-    return model_spec_from_config(read_config_json(folder))
+    raw = read_config_json(folder)
+    if resolve_architecture(raw).reads_tensor_shapes:
+        return model_spec_from_config(raw, folder_tensor_shapes(folder))
+    return model_spec_from_config(raw)
 
 
 def _register_stock_architectures() -> None:
@@ -89,12 +117,17 @@ def _register_stock_architectures() -> None:
     from .pipesun import ARCHITECTURE as PIPESUN, PipesunConfig
 
     register_architecture(PIPESUN, lambda raw: PipesunConfig.from_dict(raw).to_model_spec())
+    from .dutivik import ARCHITECTURE as DUTIVIK, DutivikConfig
+
+    register_architecture(DUTIVIK, lambda raw, shapes=None: DutivikConfig.from_dict(raw, shapes).to_model_spec(),
+                          reads_tensor_shapes=True)
 
 
 _register_stock_architectures()
 
 __all__ = [
     "ArchitectureEntry",
+    "folder_tensor_shapes",
     "model_spec_from_config",
     "model_spec_from_folder",
     "register_architecture",

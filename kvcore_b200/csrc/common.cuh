@@ -162,6 +162,13 @@ struct KvbTrace {
 #define KVB_TAG_FLASH_DIMS 34
 #define KVB_TAG_FLASH_DIMS_COMBINE 35
 #define KVB_TAG_GATHER_CACHED 36
+#define KVB_TAG_GLA_SCAN 37
+#define KVB_TAG_DELTA_SCAN 38
+#define KVB_TAG_CONV_PREPARE 39
+#define KVB_TAG_GATED_NORM 40
+#define KVB_TAG_TURN_NORM 41
+#define KVB_TAG_HEAD_GATE 42
+#define KVB_TAG_EMBED_SCALED 43
 
 // 1 when launches should carry the programmatic-serialization attribute (set by the host side).
 extern "C" int kvb_pdl_enabled();

@@ -87,6 +87,16 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_sigmoid_gate_mul": [_vp, _vp, _ll, _ll, _vp, _ll, _int, _int, _int, _int, _vp],
         "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
                                  _int, _vp, _vp, _vp, _int, _vp],
+        "kvb_gla_scan": [_vp, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _float,
+                         _float, _int, _vp],
+        "kvb_delta_scan": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _int, _vp],
+        "kvb_conv_prepare": [_vp, _vp, _ll, _vp, _int, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int,
+                             _int, _int, _int, _int, _float, _float, _int, _vp],
+        "kvb_gated_rms_norm": [_vp, _ll, _vp, _vp, _ll, _vp, _int, _int, _int, _float, _float, _int, _vp],
+        "kvb_turn_norm_kv_write": [_vp, _ll, _vp, _int, _vp, _vp, _int, _float, _vp, _vp, _vp, _int, _vp, _int, _int,
+                                   _int, _int, _int, _int, _int, _int, _int, _vp],
+        "kvb_head_gate": [_vp, _ll, _vp, _vp, _ll, _int, _int, _int, _float, _int, _vp],
+        "kvb_embed_scaled": [_vp, _vp, _vp, _int, _int, _int, _float, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
         "kvb_feed_tokens": [_vp, _vp, _vp, _int, _int, _vp],
         "kvb_read_status": [_int, ctypes.POINTER(ctypes.c_int)],
@@ -658,13 +668,14 @@ _stream_scratch: dict[int, torch.Tensor] = {}
 
 TRACE_TAGS = {27: "rms_norm_shift", 28: "stream_add_norm", 29: "attention_dims_rows", 30: "latent_prepare",
               31: "head_norm_kv_write", 32: "maps_combine", 33: "sigmoid_gate_mul", 34: "flash_dims",
-              35: "flash_dims_combine", 36: "gather_cached_rows", 25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
+              35: "flash_dims_combine", 36: "gather_cached_rows", 37: "gla_scan", 38: "delta_scan", 39: "conv_prepare",
+              40: "gated_rms_norm", 41: "turn_norm_kv_write", 42: "head_gate", 43: "embed_scaled", 25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
               22: "moe_align", 23: "moe_gemm", 24: "moe_combine", 1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
               11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
 _TRACE_UNITS = ("elementwise", "attention_decode_tma", "attention_flash", "attention_generic",
                 "attention_prefill_tc5", "gemm_f32", "sampling", "gemm_stream", "layer_norm", "qk_prepare", "moe", "attention_kept_first",
-                "stream_norm", "attention_dims", "mixer_prepare", "attention_flash_dims")
+                "stream_norm", "attention_dims", "mixer_prepare", "attention_flash_dims", "recurrence", "turn_norm")
 _trace_buffer: torch.Tensor | None = None
 
 
@@ -1294,6 +1305,167 @@ def heads_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None
 
 
 QK_NORM_MODES = {None: 0, "none": 0, "projection": 1, "head": 2}
+
+
+# ---- mixers with a matrix state per request and head, and attention with turned, normed q and k ------------
+def embed_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
+    """``table[ids] * scale`` as the first value of a 32-bit residual stream ``[T, width]``."""
+    _check(table, "table")
+    _check(ids, "ids", dtype=torch.int32)
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    _call("kvb_embed_scaled", out.data_ptr(), table.data_ptr(), ids.data_ptr(), ids.numel(), table.shape[0],
+          table.shape[1], float(scale), _dtype_code(table), _stream())
+    return out
+
+
+def turn_norm_kv_write(rows: torch.Tensor, inv_freq: torch.Tensor | None, rot: int, ctx, table: torch.Tensor,
+                       cache: torch.Tensor, *, q_heads: int, k_heads: int, dim: int, value_width: int,
+                       norm: bool = True, eps: float = 0.0, q_weight: torch.Tensor | None = None,
+                       k_weight: torch.Tensor | None = None, write: bool = True) -> None:
+    """q ``[q_heads, dim]`` and k ``[k_heads, dim]`` at the start of each row of ``rows`` (a view; last stride 1),
+    then ``value_width`` value entries.  The first ``rot`` entries of every head turn in neighbouring pairs
+    (2i, 2i+1) by ``position * inv_freq[i]``; then (``norm``) every head is divided by
+    ``sqrt(mean(x^2) + eps)`` (times ``q_weight`` / ``k_weight [dim]`` when given).  q is replaced in place;
+    with ``write`` the keys and the values go side by side into the token's row of ``cache``
+    ``[pages, 1, page, k_heads * dim + value_width]``."""
+    _check(rows, "rows", contiguous=False)
+    _check(cache, "cache", dtype=rows.dtype)
+    _check(table, "block table", dtype=torch.int32, contiguous=False)
+    tokens = rows.shape[0]
+    if rows.stride(1) != 1 or rows.shape[1] < (q_heads + k_heads) * dim + value_width:
+        raise KernelError(f"turn_norm_kv_write: rows {tuple(rows.shape)} do not hold the heads and the values")
+    rot = int(rot) if inv_freq is not None else 0
+    if rot:
+        _check(inv_freq, "inv_freq", dtype=torch.float32)
+        if rot % 2 or rot > dim or inv_freq.numel() < rot // 2:
+            raise KernelError(f"turn_norm_kv_write: {rot} turned entries of {dim} with {inv_freq.numel()} frequencies")
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _check(w, name, dtype=rows.dtype)
+            if w.numel() != dim:
+                raise KernelError(f"turn_norm_kv_write: {name} has {w.numel()} entries for heads of {dim}")
+    num_pages, one, page_size, width = cache.shape
+    if one != 1 or width != k_heads * dim + value_width or table.stride(1) != 1:
+        raise KernelError(f"turn_norm_kv_write: cache {tuple(cache.shape)} does not hold rows of "
+                          f"{k_heads} x {dim} + {value_width}")
+    _call("kvb_turn_norm_kv_write", rows.data_ptr(), rows.stride(0), None if not rot else inv_freq.data_ptr(), rot,
+          None if q_weight is None else q_weight.data_ptr(), None if k_weight is None else k_weight.data_ptr(),
+          int(bool(norm)), float(eps), ctx.positions.data_ptr(), ctx.req_index.data_ptr(), table.data_ptr(),
+          table.stride(0), cache.data_ptr(), page_size, num_pages, int(bool(write)), tokens, q_heads, k_heads, dim,
+          value_width, _dtype_code(rows), _stream())
+
+
+def head_gate(o: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """``out[t, h * V + j] = o[t, h, j] * sigmoid(gate[t, h]) * scale``: ``o [T, H, V]`` 32-bit, ``gate [T, H]``
+    and ``out [T, H * V]`` views of the activation type (last stride 1).  ``gate`` None: the scale alone."""
+    _check(o, "o", dtype=torch.float32)
+    _check(out, "out", contiguous=False)
+    tokens, heads, width = o.shape
+    if tuple(out.shape) != (tokens, heads * width) or (tokens and out.stride(1) != 1):
+        raise KernelError(f"head_gate: out {tuple(out.shape)} does not fit o {tuple(o.shape)}")
+    if gate is not None:
+        _check(gate, "gate", dtype=out.dtype, contiguous=False)
+        if tuple(gate.shape) != (tokens, heads) or (tokens and gate.stride(1) != 1):
+            raise KernelError(f"head_gate: gate {tuple(gate.shape)} does not fit o {tuple(o.shape)}")
+    _call("kvb_head_gate", out.data_ptr(), out.stride(0), o.data_ptr(), None if gate is None else gate.data_ptr(),
+          0 if gate is None else gate.stride(0), tokens, heads, width, float(scale), _dtype_code(out), _stream())
+    return out
+
+
+def _state_row(state: torch.Tensor, offset: int, need: int) -> None:
+    _check(state, "state", dtype=torch.float32)
+    if state.dim() != 2 or offset < 0 or offset + need > state.shape[1]:
+        raise KernelError(f"state {tuple(state.shape)} has no room for {need} entries at {offset}")
+
+
+def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor, state: torch.Tensor, ctx, *,
+             heads: int, dim: int, value_dim: int, q_scale: float, tau: float, state_offset: int = 0) -> torch.Tensor:
+    """Gated linear attention over the step's tokens, request by request in order:
+    ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_t * q_scale)`` with ``a_t = sigmoid(z_t)^(1/tau)``.
+    ``q, k [T, heads * dim]`` and ``v [T, heads * value_dim]`` are views of one tensor of projected rows,
+    ``z [T, heads * dim]`` the decay's logits; ``state [slots, n]`` (32-bit) holds each request's
+    ``S [heads, dim, value_dim]`` at ``state_offset`` of its slot's row and is brought up to date.
+    Returns ``o [T, heads, value_dim]`` 32-bit."""
+    for name, t in (("q", q), ("k", k), ("v", v), ("z", z)):
+        _check(t, name, dtype=q.dtype, contiguous=False)
+        if t.stride(1) != 1 or t.shape[0] != q.shape[0]:
+            raise KernelError(f"gla_scan: {name} {tuple(t.shape)} is not a view of the step's rows")
+    if q.stride(0) != k.stride(0) or q.stride(0) != v.stride(0):
+        raise KernelError("gla_scan: q, k and v must be views of one tensor of rows")
+    if q.shape[1] != heads * dim or k.shape[1] != heads * dim or v.shape[1] != heads * value_dim or z.shape[1] != heads * dim:
+        raise KernelError("gla_scan: widths do not match the head layout")
+    _state_row(state, state_offset, heads * dim * value_dim)
+    out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
+    _call("kvb_gla_scan", out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), z.data_ptr(),
+          z.stride(0), state.data_ptr(), state.stride(0), state_offset, ctx.query_start.data_ptr(),
+          ctx.state_slots.data_ptr(), ctx.num_reqs, heads, dim, value_dim, float(q_scale), float(tau), _dtype_code(q),
+          _stream())
+    return out
+
+
+def conv_prepare(rows: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, ctx, a_log: torch.Tensor,
+                 dt_bias: torch.Tensor, *, heads: int, kv_heads: int, dim: int, value_dim: int, b_col: int, a_col: int,
+                 q_scale: float, unit_eps: float, state_offset: int) -> torch.Tensor:
+    """What a delta-rule mixer does to its projections before the scan.  ``rows`` (a view; last stride 1): q and k
+    ``[kv_heads, dim]`` each, v ``[heads, value_dim]`` in the first columns (the convolved channels), one column a
+    head at ``b_col`` and at ``a_col``.  Channels pass a causal convolution over time (``taps [channels, C]``, the
+    last tap on the current token; the ``C - 1`` inputs in front of a portion are the request's
+    ``state[slot, state_offset:][channels, C - 1]``, brought up to date by this call) and SiLU; q and k become
+    unit vectors per head (``x / sqrt(sum(x^2) + unit_eps)``, q times ``q_scale``); ``beta = sigmoid(b)``;
+    ``gate = exp(-exp(a_log) * softplus(a + dt_bias))``.  Returns 32-bit ``[T, q | k | v | beta | gate]``."""
+    _check(rows, "rows", contiguous=False)
+    _check(taps, "taps", dtype=rows.dtype)
+    _check(a_log, "a_log", dtype=rows.dtype)
+    _check(dt_bias, "dt_bias", dtype=rows.dtype)
+    channels = 2 * kv_heads * dim + heads * value_dim
+    if rows.stride(1) != 1 or taps.dim() != 2 or taps.shape[0] != channels or not 1 <= taps.shape[1] <= 9:
+        raise KernelError(f"conv_prepare: taps {tuple(taps.shape)} for {channels} channels (1 to 9 taps)")
+    if max(b_col, a_col) + heads > rows.shape[1] or min(b_col, a_col) < channels or a_log.numel() != heads or dt_bias.numel() != heads:
+        raise KernelError("conv_prepare: the per-head columns do not fit the rows")
+    _state_row(state, state_offset, channels * (taps.shape[1] - 1))
+    tokens = rows.shape[0]
+    out = torch.empty((tokens, channels + 2 * heads), dtype=torch.float32, device=rows.device)
+    _call("kvb_conv_prepare", out.data_ptr(), rows.data_ptr(), rows.stride(0), taps.data_ptr(), taps.shape[1],
+          state.data_ptr(), state.stride(0), state_offset, ctx.req_index.data_ptr(), ctx.query_start.data_ptr(),
+          ctx.state_slots.data_ptr(), a_log.data_ptr(), dt_bias.data_ptr(), tokens, ctx.num_reqs, heads, kv_heads, dim,
+          value_dim, b_col, a_col, float(q_scale), float(unit_eps), _dtype_code(rows), _stream(),
+          kernels=2 if taps.shape[1] > 1 else 1)
+    return out
+
+
+def delta_scan(prepared: torch.Tensor, state: torch.Tensor, ctx, *, heads: int, kv_heads: int, dim: int,
+               value_dim: int, state_offset: int = 0) -> torch.Tensor:
+    """The gated delta rule over the step's tokens, request by request in order, on what ``conv_prepare`` left:
+    ``S <- g_t S``; ``u = beta_t (v_t - S^T k_t)``; ``S <- S + k_t u^T``; ``o_t = S^T q_t`` (head ``h`` reads
+    q/k head ``h // (heads / kv_heads)``).  ``state [slots, n]`` holds ``S [heads, dim, value_dim]`` at
+    ``state_offset``.  Returns ``o [T, heads, value_dim]`` 32-bit."""
+    _check(prepared, "prepared", dtype=torch.float32)
+    if prepared.dim() != 2 or prepared.shape[1] != 2 * kv_heads * dim + heads * value_dim + 2 * heads:
+        raise KernelError(f"delta_scan: prepared rows {tuple(prepared.shape)} do not match the head layout")
+    _state_row(state, state_offset, heads * dim * value_dim)
+    out = torch.empty((prepared.shape[0], heads, value_dim), dtype=torch.float32, device=prepared.device)
+    _call("kvb_delta_scan", out.data_ptr(), prepared.data_ptr(), state.data_ptr(), state.stride(0), state_offset,
+          ctx.query_start.data_ptr(), ctx.state_slots.data_ptr(), ctx.num_reqs, heads, kv_heads, dim, value_dim,
+          _stream())
+    return out
+
+
+def gated_rms_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                   scale: float = 1.0) -> torch.Tensor:
+    """``out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]) * scale``:
+    ``o [T, H, V]`` 32-bit, ``gate`` and ``out [T, H * V]`` views of the activation type, ``weight [V]``."""
+    _check(o, "o", dtype=torch.float32)
+    _check(gate, "gate", contiguous=False)
+    _check(out, "out", dtype=gate.dtype, contiguous=False)
+    _check(weight, "weight", dtype=gate.dtype)
+    tokens, heads, width = o.shape
+    if (tuple(gate.shape) != (tokens, heads * width) or tuple(out.shape) != (tokens, heads * width)
+            or weight.numel() != width or (tokens and (gate.stride(1) != 1 or out.stride(1) != 1))):
+        raise KernelError(f"gated_rms_norm: gate {tuple(gate.shape)} / out {tuple(out.shape)} / weight do not fit "
+                          f"o {tuple(o.shape)}")
+    _call("kvb_gated_rms_norm", out.data_ptr(), out.stride(0), o.data_ptr(), gate.data_ptr(), gate.stride(0),
+          weight.data_ptr(), tokens, heads, width, float(eps), float(scale), _dtype_code(out), _stream())
+    return out
 
 
 def qk_prepare(rows: torch.Tensor, positions: torch.Tensor, req_index: torch.Tensor, cos_sin: torch.Tensor | None,

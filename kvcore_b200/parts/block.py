@@ -76,7 +76,9 @@ class ParallelResidualBlock(Block):
     """Mixer and feed-forward side by side on one stream: ``x <- x + (mixer(norm_a(x)) + ff(norm_b(x)))``,
     both norms reading the same ``x``.  The stream ``x`` is kept in 32-bit whatever the activation type:
     the two sub-layer outputs are added to each other and then to the stream in 32-bit by one kernel.
-    A layer without a feed-forward (``layer.feed_forward is None``) adds the mixer alone.
+    A layer without a feed-forward (``layer.feed_forward is None``) adds the mixer alone.  A layer whose
+    norms name no ``feed_forward_norm`` has one norm, and both sub-layers read its output:
+    ``h = norm(x)``, ``x <- x + (mixer(h) + ff(h))``.
 
     In the ``(h, residual)`` pair that runs through the blocks this block returns ``(Summed, stream)``."""
 
@@ -85,7 +87,8 @@ class ParallelResidualBlock(Block):
         self.mixer = MIXERS.build(layer.mixer, dtype=dtype, device=device)
         self.feed_forward = self.feed_forward_norm = None
         if layer.feed_forward is not None:
-            self.feed_forward_norm = NORMS.build(layer.norms["feed_forward_norm"], dtype=dtype, device=device)
+            if "feed_forward_norm" in layer.norms:
+                self.feed_forward_norm = NORMS.build(layer.norms["feed_forward_norm"], dtype=dtype, device=device)
             self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, dtype=dtype, device=device)
 
     def parts(self):
@@ -107,12 +110,14 @@ class ParallelResidualBlock(Block):
         # Both sub-layers read the same stream, so a feed-forward that has something to get ready (a
         # ``prepare(x, ctx)`` whose result ``forward`` takes: a router whose grouping the host must see)
         # does that ahead of the mixer's launches, and nothing waits for it later.
-        fx = prepared = None
+        fx = prepared = mx = None
         if self.feed_forward is not None:
-            fx = self.feed_forward_norm.forward(stream)
+            fx = mx = (self.feed_forward_norm or self.mixer_norm).forward(stream)
             prepare = getattr(self.feed_forward, "prepare", None)
             prepared = None if prepare is None else prepare(fx, ctx)
-        a = self.mixer.forward(self.mixer_norm.forward(stream), ctx, cache)
+        if mx is None or self.feed_forward_norm is not None:
+            mx = self.mixer_norm.forward(stream)
+        a = self.mixer.forward(mx, ctx, cache)
         f = None
         if self.feed_forward is not None:
             f = (self.feed_forward.forward(fx, ctx) if prepared is None

@@ -17,10 +17,13 @@ class TokenEmbedding(Part):
     graph_safe = True
 
     def __init__(self, *, vocab_size: int, hidden_size: int, name: str, tensor: str | None = None,
-                 dtype, device) -> None:
+                 scale: float | None = None, dtype, device) -> None:
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
         self.name = name
+        # ``scale``: the embedded tokens are ``table[id] * scale``, formed in 32-bit; the result is then the
+        # first value of a 32-bit residual stream rather than rows of the activation type
+        self.scale = None if scale is None else float(scale)
         self.tensor = tensor or f"{name}.weight"     # the table's full checkpoint name
         self.weight = torch.empty(self.vocab_size, self.hidden_size, dtype=dtype, device=device)
 
@@ -28,6 +31,8 @@ class TokenEmbedding(Part):
         return [WeightSlot(self.tensor, self.weight)]
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        if self.scale is not None:
+            return K.embed_scaled(self.weight, token_ids, self.scale)
         return K.gather_rows(self.weight, token_ids)
 
 

@@ -13,7 +13,8 @@ import torch
 
 from .. import kernels as K
 from ..config.model_spec import ModelSpec
-from . import attention, attention_maps, block, embedding, mlp, moe, norm, rope  # noqa: F401  (register the stock parts)
+from . import (attention, attention_maps, block, embedding, mlp, moe, norm, recurrent, rope,  # noqa: F401
+               side_by_side)                                                                 # (register the stock parts)
 from .base import BLOCKS, EMBEDDINGS, LM_HEADS, NORMS, CacheSpec, StateSpec, Summed, WeightSlot
 
 

@@ -439,6 +439,126 @@ def linear_add_residual(x, weight, bias, residual):
     return linear(x, weight, bias), None
 
 
+# ---- mixers with a matrix state, turned and normed attention inputs ------------------------------------
+def embed_scaled(table, ids, scale):
+    return table[ids.long()].float() * scale
+
+
+def turn_norm_kv_write(rows, inv_freq, rot, ctx, table, cache, *, q_heads, k_heads, dim, value_width, norm=True,
+                       eps=0.0, q_weight=None, k_weight=None, write=True):
+    tokens = rows.shape[0]
+    page_size = cache.shape[2]
+    qc, kc = q_heads * dim, k_heads * dim
+    rot = rot if inv_freq is not None else 0
+
+    def prepare(x, weight):                       # [T, heads, dim] float
+        x = x.clone()
+        if rot:
+            angle = ctx.positions.float()[:, None, None] * inv_freq[: rot // 2].float()
+            cos, sin = torch.cos(angle), torch.sin(angle)
+            even, odd = x[..., 0:rot:2].clone(), x[..., 1:rot:2].clone()
+            x[..., 0:rot:2] = even * cos - odd * sin
+            x[..., 1:rot:2] = odd * cos + even * sin
+        if norm:
+            x = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+        return x if weight is None else x * weight.float()
+
+    q = prepare(rows[:, :qc].float().reshape(tokens, q_heads, dim), q_weight)
+    k = prepare(rows[:, qc:qc + kc].float().reshape(tokens, k_heads, dim), k_weight).to(rows.dtype)
+    rows[:, :qc] = q.to(rows.dtype).reshape(tokens, qc)
+    if not write:
+        return
+    for t in range(tokens):
+        pos = int(ctx.positions[t])
+        page = int(table[int(ctx.req_index[t]), pos // page_size])
+        assert page > 0
+        cache[page, 0, pos % page_size, :kc] = k[t].reshape(kc)
+        cache[page, 0, pos % page_size, kc:] = rows[t, qc + kc:qc + kc + value_width]
+
+
+def head_gate(o, gate, out, scale=1.0):
+    tokens, heads, width = o.shape
+    factor = scale if gate is None else torch.sigmoid(gate.float())[:, :, None] * scale
+    out.copy_((o * factor).reshape(tokens, heads * width).to(out.dtype))
+    return out
+
+
+def _request_ranges(ctx):
+    starts = [int(x) for x in ctx.query_start]
+    return [(r, starts[r], starts[r + 1], int(ctx.state_slots[r])) for r in range(ctx.num_reqs)]
+
+
+def gla_scan(q, k, v, z, state, ctx, *, heads, dim, value_dim, q_scale, tau, state_offset=0):
+    tokens = q.shape[0]
+    out = torch.empty((tokens, heads, value_dim), dtype=torch.float32, device=q.device)
+    n = heads * dim * value_dim
+    alpha = torch.exp(torch.nn.functional.logsigmoid(z.float()) / tau).reshape(tokens, heads, dim)
+    qf = q.float().reshape(tokens, heads, dim) * q_scale
+    kf, vf = k.float().reshape(tokens, heads, dim), v.float().reshape(tokens, heads, value_dim)
+    for _, begin, end, slot in _request_ranges(ctx):
+        S = state[slot, state_offset:state_offset + n].reshape(heads, dim, value_dim).clone()
+        for t in range(begin, end):
+            S = S * alpha[t][:, :, None] + kf[t][:, :, None] * vf[t][:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, qf[t])
+        state[slot, state_offset:state_offset + n] = S.reshape(n)
+    return out
+
+
+def conv_prepare(rows, taps, state, ctx, a_log, dt_bias, *, heads, kv_heads, dim, value_dim, b_col, a_col, q_scale,
+                 unit_eps, state_offset):
+    tokens = rows.shape[0]
+    channels, num_taps = taps.shape
+    keep = num_taps - 1
+    qk = kv_heads * dim
+    out = torch.empty((tokens, channels + 2 * heads), dtype=torch.float32, device=rows.device)
+    x = rows[:, :channels].float()
+    for _, begin, end, slot in _request_ranges(ctx):
+        held = state[slot, state_offset:state_offset + channels * keep].reshape(channels, keep)
+        history = torch.cat([held.T.clone(), x[begin:end]])            # [keep + n, channels]
+        acc = torch.zeros((end - begin, channels))
+        for j in range(num_taps):
+            acc = acc + history[j:j + end - begin] * taps[:, j].float()
+        out[begin:end, :channels] = acc * torch.sigmoid(acc)
+        if keep:
+            state[slot, state_offset:state_offset + channels * keep] = history[-keep:].T.reshape(-1)
+    for lo, scale in ((0, q_scale), (qk, 1.0)):
+        vec = out[:, lo:lo + qk].reshape(tokens, kv_heads, dim)
+        out[:, lo:lo + qk] = (vec / torch.sqrt(vec.pow(2).sum(-1, keepdim=True) + unit_eps) * scale).reshape(tokens, qk)
+    out[:, channels:channels + heads] = torch.sigmoid(rows[:, b_col:b_col + heads].float())
+    step = torch.nn.functional.softplus(rows[:, a_col:a_col + heads].float() + dt_bias.float())
+    out[:, channels + heads:] = torch.exp(-torch.exp(a_log.float()) * step)
+    return out
+
+
+def delta_scan(prepared, state, ctx, *, heads, kv_heads, dim, value_dim, state_offset=0):
+    tokens = prepared.shape[0]
+    qk, n = kv_heads * dim, heads * dim * value_dim
+    share = torch.arange(heads) // (heads // kv_heads)
+    q = prepared[:, :qk].reshape(tokens, kv_heads, dim)[:, share]
+    k = prepared[:, qk:2 * qk].reshape(tokens, kv_heads, dim)[:, share]
+    v = prepared[:, 2 * qk:2 * qk + heads * value_dim].reshape(tokens, heads, value_dim)
+    beta = prepared[:, 2 * qk + heads * value_dim:][:, :heads]
+    gate = prepared[:, 2 * qk + heads * value_dim + heads:]
+    out = torch.empty((tokens, heads, value_dim), dtype=torch.float32, device=prepared.device)
+    for _, begin, end, slot in _request_ranges(ctx):
+        S = state[slot, state_offset:state_offset + n].reshape(heads, dim, value_dim).clone()
+        for t in range(begin, end):
+            S = S * gate[t][:, None, None]
+            u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, k[t]))
+            S = S + k[t][:, :, None] * u[:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, q[t])
+        state[slot, state_offset:state_offset + n] = S.reshape(n)
+    return out
+
+
+def gated_rms_norm(o, gate, weight, eps, out, scale=1.0):
+    tokens, heads, width = o.shape
+    g = gate.float().reshape(tokens, heads, width)
+    y = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight.float() * (g * torch.sigmoid(g)) * scale
+    out.copy_(y.reshape(tokens, heads * width).to(out.dtype))
+    return out
+
+
 # ---- sampling: the same counter-based noise as the CUDA kernel --------------------------------
 def philox4x32_10(counter, key):
     c = [np.uint64(x) for x in counter]
@@ -497,6 +617,7 @@ _NAMES = [
     "add_rmsnorm", "silu_mul", "rope_inplace", "rope_table", "rope_kv_write", "paged_attention", "linear", "linear_silu_mul", "norm_linear", "linear_add_residual", "sample",
     "rms_norm_shift", "stream_add_norm", "attention_dims", "latent_prepare", "head_norm_kv_write", "maps_combine",
     "sigmoid_gate_mul", "heads_linear", "gather_cached_rows",
+    "embed_scaled", "turn_norm_kv_write", "head_gate", "gla_scan", "conv_prepare", "delta_scan", "gated_rms_norm",
     "layer_norm", "stream_add", "qk_prepare", "glu_clamped", "moe_route", "moe_experts", "moe_combine", "moe_path",
 ]
 
