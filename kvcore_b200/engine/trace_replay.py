@@ -86,6 +86,8 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="tokens the cache pool is made for")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
+    parser.add_argument("--max-live", type=int, default=4,
+                        help="requests that are live at one time: state slots and block-table rows")
     parser.add_argument("--device", default="cuda:0")
     parser.add_argument("--fill-freed-pages", choices=["zero", "poison"], default=None,
                         help="debugging aid: overwrite pages that nobody holds any more before the next step")
@@ -93,8 +95,8 @@ def main(argv: list[str] | None = None) -> int:
 
     K.ensure_built(verbose=True)
     step_function, kv = build_replay(
-        args.model, args.dtype, args.max_tokens, page_size=args.block_size, device=args.device,
-        fill_freed_pages=args.fill_freed_pages,
+        args.model, args.dtype, args.max_tokens, page_size=args.block_size, max_live=args.max_live,
+        device=args.device, fill_freed_pages=args.fill_freed_pages,
     )
 
     def report(text: str) -> None:
