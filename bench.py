@@ -647,6 +647,28 @@ def pipesun_config(size: dict, kinds: str) -> dict:
             "layers": layers}
 
 
+def dutivik_config(size: dict, kinds: str) -> dict:
+    """A Dutivik config.json of ``DESIGN_LAYERS`` layers.  ``kinds``: a letter per layer, "g" gated linear
+    attention (half of Llama's heads, values twice as wide as the keys, a decay projection of 16 inside),
+    "p" sliding-window attention (half of Llama's heads, a window of 1,024) beside the gated delta rule
+    (half of Llama's heads, two value heads a key head, four taps).  Either layer's projections together
+    have about the size of Llama's attention projections."""
+    half, kv_half, dim = size["heads"] // 2, max(1, size["kv_heads"] // 2), size["dim"]
+    layers = []
+    for kind in (kinds * DESIGN_LAYERS)[:DESIGN_LAYERS]:
+        if kind == "g":
+            layers.append({"type": "gla", "mlp": {"kind": "dense", "ff": size["ff"]},
+                           "mixer": {"heads": half, "dim": dim, "vdim": 2 * dim, "tau": 16.0, "decay_rank": 16}})
+            continue
+        left = {"heads": half, "kv_heads": kv_half, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 4.0}}}
+        right = {"heads": half, "kv_heads": half // 2, "dim": dim, "vdim": dim, "conv": 4}
+        layers.append({"type": "parallel", "mlp": {"kind": "dense", "ff": size["ff"]},
+                       "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}})
+    return {"architecture": "Dutivik", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": float(size["width"]) ** 0.5}, "layers": layers}
+
+
 def llama_config(size: dict) -> dict:
     return dict(LLAMA_31_8B, hidden_size=size["width"], intermediate_size=size["ff"], num_hidden_layers=DESIGN_LAYERS,
                 num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["dim"],
@@ -697,6 +719,12 @@ def compare_designs(args) -> int:
                 "toposun_dense_full_window": toposun_config(size, "dense", 1 << 20, 0),
                 "toposun_dense": toposun_config(size, "dense", 1024, 4),
                 "toposun_moe": toposun_config(size, "moe", 1024, 4),
+            })
+        elif args.designs_of == "dutivik":
+            models.update({
+                "dutivik_linear": dutivik_config(size, "g"),
+                "dutivik_side_by_side": dutivik_config(size, "p"),
+                "dutivik_mixed": dutivik_config(size, "gppp"),
             })
         else:
             models.update({
@@ -772,7 +800,7 @@ def main() -> int:
     parser.add_argument("--designs", action="store_true",
                         help="instead: Toposun (dense and mixture feed-forward) beside a Llama of equal layer sizes, "
                              "prefill and decode throughput and each kernel's share of a step; prints a line of its own")
-    parser.add_argument("--designs-of", default="toposun", choices=["toposun", "pipesun"],
+    parser.add_argument("--designs-of", default="toposun", choices=["toposun", "pipesun", "dutivik"],
                         help="which design --designs sets beside Llama")
     parser.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="one size of --designs")
     args = parser.parse_args()

@@ -169,6 +169,7 @@ struct KvbTrace {
 #define KVB_TAG_TURN_NORM 41
 #define KVB_TAG_HEAD_GATE 42
 #define KVB_TAG_EMBED_SCALED 43
+#define KVB_TAG_GLA_PREPARE 44
 
 // 1 when launches should carry the programmatic-serialization attribute (set by the host side).
 extern "C" int kvb_pdl_enabled();

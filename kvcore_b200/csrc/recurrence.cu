@@ -6,13 +6,18 @@
 //   over the request's tokens of this step in order.
 //     decay per key channel (gated linear attention):
 //         S <- diag(a_t) S + k_t v_t^T,                 o_t = S^T q_t
-//         with a_t = sigmoid(z_t)^(1/tau) and q_t scaled by `q_scale`, both formed here from the projections;
+//         with a_t = sigmoid(z_t)^(1/tau) and q_t scaled by `q_scale`, as `gla_prepare` left them (32-bit);
 //     delta rule with one decay per head:
 //         S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
 //         with q_t, k_t, v_t, beta_t, g_t as `conv_prepare` left them (32-bit).
-//   A thread owns one column of S (all D rows, or D / RSPLIT of them with its RSPLIT - 1 neighbours) in
-//   registers; columns never exchange anything, so any cut of a request into steps gives the same bits.
-//   The tokens' vectors go through shared memory a batch at a time, shared by the block's columns.
+//   A column of S is shared by RSPLIT neighbouring lanes (16 rows each, in registers; RSPLIT follows from the
+//   key width alone), a block owns 128 / RSPLIT columns of one (request, head): a single prompt already fills
+//   the machine with H * V * RSPLIT / 128 blocks, and a decode step reads and writes every state once.
+//   Columns never exchange anything and the lanes of a column sum in a fixed order, so any cut of a request
+//   into steps gives the same bits.  The tokens' vectors (32-bit: q, k, and the decays or beta and gate) come
+//   through two stages of shared memory by cp.async, a few tokens a stage, the next stage in flight while this
+//   one is computed.  gla_prepare writes those vectors for the decay-per-channel form (q times its scale, k,
+//   a = sigmoid(z)^(1/tau)) once a token, so the blocks that share a head do not each take the exponentials.
 //
 //   conv_prepare (delta rule): a short causal convolution over time per channel on the q, k and v
 //   projections (taps [channels, C], the last tap on the current token; the C - 1 inputs in front of a
@@ -23,16 +28,24 @@
 //   gated_rms_norm: out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight * silu(gate[t, h, :]) * scale.
 #include "common.cuh"
 
-#define SCAN_MAX_THREADS 256
+#define SCAN_THREADS 128
+#define SCAN_DREG 16
 
-template <typename T>
-__device__ __forceinline__ float load_as_float(const T* p, long long i) { return to_float(p[i]); }
+__device__ __forceinline__ void scan_copy16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void scan_copy4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void scan_copies_done() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 
 struct ScanParams {
-  // per token and head: q, k [D] and v [V] at base + t * token_stride + h * head_stride (head h of q and k
-  // reads head h / kv_share)
-  const void* q; const void* k; const void* v; const void* z;
-  long long q_token, q_head, k_token, k_head, v_token, v_head, z_token, z_head;
+  // 32-bit vectors per token: q and k [D] of head h / kv_share, and (decay per key channel) the decays a [D]
+  // of head h, each at base + t * vec_token + head * D
+  const float* q; const float* k; const float* a;
+  long long vec_token;
+  int vec16;                                // every vector starts on a 16-byte boundary and D is a multiple of 4
+  const void* v; long long v_token;         // values [V] of head h at v + t * v_token + h * V (elements)
   const float* beta; const float* gate;     // [T, H] with row stride bg_stride (delta rule)
   long long bg_stride;
   float* out;                               // [T, H, V]
@@ -40,166 +53,240 @@ struct ScanParams {
   long long state_stride, state_offset;
   const int* query_start; const int* state_slots;
   int heads, kv_share, D, V;
-  float q_scale, inv_tau;
-  int batch;                                // tokens a trip through shared memory holds
 };
 
-// MODE 0: decay per key channel; MODE 1: delta rule.  DREG rows a thread; RSPLIT threads a column.
-template <typename TIN, int MODE, int DREG, int RSPLIT>
-__global__ void __launch_bounds__(SCAN_MAX_THREADS)
+// MODE 0: decay per key channel; MODE 1: delta rule.  RSPLIT threads a column of S, SCAN_DREG rows each;
+// BATCH tokens a stage of shared memory.
+template <typename TV, int MODE, int RSPLIT, int BATCH>
+__global__ void __launch_bounds__(SCAN_THREADS)
 state_scan_kernel(ScanParams p) {
   KVB_KERNEL_PROLOGUE(MODE == 0 ? KVB_TAG_GLA_SCAN : KVB_TAG_DELTA_SCAN);
-  extern __shared__ float smem[];
-  constexpr int DP = DREG * RSPLIT;           // rows covered (>= D; rows beyond D stay zero)
-  const int req = blockIdx.x, h = blockIdx.y;
-  const int cols = blockDim.x / RSPLIT;       // columns this block owns
-  const int col = blockIdx.z * cols + threadIdx.x / RSPLIT;
-  const int part = threadIdx.x % RSPLIT;      // which DREG rows of the column
-  const int row0 = part * DREG;
+  extern __shared__ __align__(16) float smem[];
+  constexpr int DP = SCAN_DREG * RSPLIT;            // rows covered (>= D; rows beyond D stay zero)
+  constexpr int COLS = SCAN_THREADS / RSPLIT;       // columns this block owns
+  constexpr int NVEC = MODE == 0 ? 3 : 2;           // q, k (, a)
+  constexpr int TOKEN = NVEC * DP + 4;              // floats a token holds in a stage; the last four: beta, gate
+  constexpr int STAGE = BATCH * TOKEN;
+  constexpr int VPT = (BATCH * COLS + SCAN_THREADS - 1) / SCAN_THREADS;
+  float* const vectors = smem;                      // [2][BATCH][TOKEN]
+  float* const values = smem + 2 * STAGE;           // [2][BATCH][COLS]
+
+  const int req = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int part = tid % RSPLIT, c = tid / RSPLIT;
+  const int col = blockIdx.z * COLS + c;
   const int begin = p.query_start[req], end = p.query_start[req + 1];
   const int D = p.D, V = p.V;
   const bool live = col < V;
-  float* qs = smem;                           // [batch][DP]
-  float* ks = qs + (size_t)p.batch * DP;
-  float* as = ks + (size_t)p.batch * DP;      // MODE 0: decays [batch][DP]; MODE 1: beta, gate [batch][2]
-  float* vs = as + (size_t)p.batch * (MODE == 0 ? DP : 2);   // [batch][cols]
-
-  float* S_global = p.state + (size_t)p.state_slots[req] * p.state_stride + p.state_offset + (size_t)h * D * V;
-  float S[DREG];
-#pragma unroll
-  for (int i = 0; i < DREG; ++i) S[i] = (live && row0 + i < D) ? S_global[(size_t)(row0 + i) * V + col] : 0.0f;
-
-  const TIN* qg = (const TIN*)p.q; const TIN* kg = (const TIN*)p.k; const TIN* vg = (const TIN*)p.v;
-  const TIN* zg = (const TIN*)p.z;
   const int kvh = h / p.kv_share;
-  for (int t0 = begin; t0 < end; t0 += p.batch) {
-    const int nb = min(p.batch, end - t0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < nb * DP; e += blockDim.x) {
-      const int tt = e / DP, i = e % DP;
-      const long long t = t0 + tt;
-      float qv = 0.0f, kv = 0.0f, av = 1.0f;
-      if (i < D) {
-        qv = load_as_float(qg, t * p.q_token + (long long)kvh * p.q_head + i) * p.q_scale;
-        kv = load_as_float(kg, t * p.k_token + (long long)kvh * p.k_head + i);
-        if (MODE == 0) {
-          // sigmoid(z)^(1/tau) = exp(log_sigmoid(z) / tau); log_sigmoid(z) = min(z, 0) - log1p(exp(-|z|))
-          const float zv = load_as_float(zg, t * p.z_token + (long long)h * p.z_head + i);
-          av = expf((fminf(zv, 0.0f) - log1pf(expf(-fabsf(zv)))) * p.inv_tau);
-        }
-      }
-      qs[e] = qv; ks[e] = kv;
-      if (MODE == 0) as[e] = av;
+  const TV* vg = (const TV*)p.v;
+
+  // Thread `part` of a column holds rows (j * RSPLIT + part) * 4 + m, j and m in 0..3: for one j the parts of a
+  // column read neighbouring 16-byte pieces of a vector.
+  float* S_global = p.state + (size_t)p.state_slots[req] * p.state_stride + p.state_offset + (size_t)h * D * V;
+  float S[SCAN_DREG];
+#pragma unroll
+  for (int i = 0; i < SCAN_DREG; ++i) {
+    const int row = ((i >> 2) * RSPLIT + part) * 4 + (i & 3);
+    S[i] = (live && row < D) ? S_global[(size_t)row * V + col] : 0.0f;
+  }
+  if (D < DP)                                       // rows beyond D read zeros whatever the stage holds
+    for (int e = tid; e < 2 * BATCH * NVEC * (DP - D); e += SCAN_THREADS) {
+      const int slot = e / (DP - D), i = D + e % (DP - D);
+      vectors[(slot / NVEC) * TOKEN + (slot % NVEC) * DP + i] = 0.0f;
     }
-    for (int e = threadIdx.x; e < nb * cols; e += blockDim.x) {
-      const int tt = e / cols, c = blockIdx.z * cols + e % cols;
-      vs[e] = c < V ? load_as_float(vg, (long long)(t0 + tt) * p.v_token + (long long)h * p.v_head + c) : 0.0f;
+
+  auto fetch = [&](int stage, int t0, int nb) {     // the vectors of tokens t0 .. t0 + nb - 1, asynchronously
+    float* dst = vectors + stage * STAGE;
+    if (p.vec16) {
+      const int pieces = D >> 2, per_token = NVEC * pieces;
+      for (int e = tid; e < nb * per_token; e += SCAN_THREADS) {
+        const int tt = e / per_token, r = e - tt * per_token, vec = r / pieces, i = (r - vec * pieces) << 2;
+        const float* base = vec == 0 ? p.q : vec == 1 ? p.k : p.a;
+        scan_copy16(dst + tt * TOKEN + vec * DP + i,
+                    base + (long long)(t0 + tt) * p.vec_token + (long long)(vec == 2 ? h : kvh) * D + i);
+      }
+    } else {
+      const int per_token = NVEC * D;
+      for (int e = tid; e < nb * per_token; e += SCAN_THREADS) {
+        const int tt = e / per_token, r = e - tt * per_token, vec = r / D, i = r - vec * D;
+        const float* base = vec == 0 ? p.q : vec == 1 ? p.k : p.a;
+        scan_copy4(dst + tt * TOKEN + vec * DP + i,
+                   base + (long long)(t0 + tt) * p.vec_token + (long long)(vec == 2 ? h : kvh) * D + i);
+      }
     }
     if (MODE == 1)
-      for (int e = threadIdx.x; e < nb; e += blockDim.x) {
-        as[2 * e] = p.beta[(size_t)(t0 + e) * p.bg_stride + h];
-        as[2 * e + 1] = p.gate[(size_t)(t0 + e) * p.bg_stride + h];
+      for (int e = tid; e < 2 * nb; e += SCAN_THREADS) {
+        const int tt = e >> 1;
+        scan_copy4(dst + tt * TOKEN + NVEC * DP + (e & 1),
+                   ((e & 1) ? p.gate : p.beta) + (size_t)(t0 + tt) * p.bg_stride + h);
       }
-    __syncthreads();
-    for (int tt = 0; tt < nb; ++tt) {
-      const float* q = qs + (size_t)tt * DP + row0;
-      const float* k = ks + (size_t)tt * DP + row0;
-      const float v = vs[tt * cols + threadIdx.x / RSPLIT];
-      float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
-      if (MODE == 0) {
-        const float* a = as + (size_t)tt * DP + row0;
+  };
+  float held[VPT];
+  auto load_values = [&](int t0, int nb) {          // this block's columns of v, into registers
 #pragma unroll
-        for (int i = 0; i < DREG; i += 4) {
-          const float4 a4 = *reinterpret_cast<const float4*>(a + i);
-          const float4 k4 = *reinterpret_cast<const float4*>(k + i);
-          const float4 q4 = *reinterpret_cast<const float4*>(q + i);
-          S[i] = fmaf(k4.x, v, a4.x * S[i]);         o0 = fmaf(S[i], q4.x, o0);
-          S[i + 1] = fmaf(k4.y, v, a4.y * S[i + 1]); o1 = fmaf(S[i + 1], q4.y, o1);
-          S[i + 2] = fmaf(k4.z, v, a4.z * S[i + 2]); o2 = fmaf(S[i + 2], q4.z, o2);
-          S[i + 3] = fmaf(k4.w, v, a4.w * S[i + 3]); o3 = fmaf(S[i + 3], q4.w, o3);
-        }
-      } else {
-        const float beta = as[2 * tt], g = as[2 * tt + 1];
-        float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
-#pragma unroll
-        for (int i = 0; i < DREG; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(k + i);
-          S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
-          d0 = fmaf(S[i], k4.x, d0); d1 = fmaf(S[i + 1], k4.y, d1);
-          d2 = fmaf(S[i + 2], k4.z, d2); d3 = fmaf(S[i + 3], k4.w, d3);
-        }
-        float dot = (d0 + d1) + (d2 + d3);
-#pragma unroll
-        for (int m = 1; m < RSPLIT; m <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
-        const float u = beta * (v - dot);
-#pragma unroll
-        for (int i = 0; i < DREG; i += 4) {
-          const float4 k4 = *reinterpret_cast<const float4*>(k + i);
-          const float4 q4 = *reinterpret_cast<const float4*>(q + i);
-          S[i] = fmaf(k4.x, u, S[i]);         o0 = fmaf(S[i], q4.x, o0);
-          S[i + 1] = fmaf(k4.y, u, S[i + 1]); o1 = fmaf(S[i + 1], q4.y, o1);
-          S[i + 2] = fmaf(k4.z, u, S[i + 2]); o2 = fmaf(S[i + 2], q4.z, o2);
-          S[i + 3] = fmaf(k4.w, u, S[i + 3]); o3 = fmaf(S[i + 3], q4.w, o3);
-        }
-      }
-      float o = (o0 + o1) + (o2 + o3);
-#pragma unroll
-      for (int m = 1; m < RSPLIT; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-      if (live && part == 0) p.out[((size_t)(t0 + tt) * p.heads + h) * V + col] = o;
+    for (int j = 0; j < VPT; ++j) {
+      const int e = tid + j * SCAN_THREADS, tt = e / COLS, cc = blockIdx.z * COLS + e % COLS;
+      held[j] = (tt < nb && cc < V) ? to_float(vg[(long long)(t0 + tt) * p.v_token + (long long)h * V + cc]) : 0.0f;
     }
+  };
+  auto store_values = [&](int stage) {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int e = tid + j * SCAN_THREADS;
+      if (e < BATCH * COLS) values[stage * BATCH * COLS + e] = held[j];
+    }
+  };
+
+  if (begin < end) {
+    fetch(0, begin, min(BATCH, end - begin));
+    load_values(begin, min(BATCH, end - begin));
+    store_values(0);
+  }
+  scan_copies_done();
+  __syncthreads();
+  int stage = 0;
+  for (int t0 = begin; t0 < end; t0 += BATCH, stage ^= 1) {
+    const int nb = min(BATCH, end - t0);
+    const int next = t0 + BATCH, next_nb = min(BATCH, end - next);
+    if (next < end) {
+      fetch(stage ^ 1, next, next_nb);
+      load_values(next, next_nb);
+    }
+    const float* st = vectors + stage * STAGE;
+    const float* vs = values + stage * BATCH * COLS;
+#pragma unroll
+    for (int tt = 0; tt < BATCH; ++tt) {
+      if (tt < nb) {
+        const float* q = st + tt * TOKEN;
+        const float* k = q + DP;
+        const float v = vs[tt * COLS + c];
+        float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+        if (MODE == 0) {
+          const float* a = k + DP;
+#pragma unroll
+          for (int j = 0; j < SCAN_DREG / 4; ++j) {
+            const int at = (j * RSPLIT + part) * 4, i = 4 * j;
+            const float4 a4 = *reinterpret_cast<const float4*>(a + at);
+            const float4 k4 = *reinterpret_cast<const float4*>(k + at);
+            const float4 q4 = *reinterpret_cast<const float4*>(q + at);
+            S[i] = fmaf(k4.x, v, a4.x * S[i]);         o0 = fmaf(S[i], q4.x, o0);
+            S[i + 1] = fmaf(k4.y, v, a4.y * S[i + 1]); o1 = fmaf(S[i + 1], q4.y, o1);
+            S[i + 2] = fmaf(k4.z, v, a4.z * S[i + 2]); o2 = fmaf(S[i + 2], q4.z, o2);
+            S[i + 3] = fmaf(k4.w, v, a4.w * S[i + 3]); o3 = fmaf(S[i + 3], q4.w, o3);
+          }
+        } else {
+          const float beta = q[NVEC * DP], g = q[NVEC * DP + 1];
+          float4 k4[SCAN_DREG / 4];
+          float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
+#pragma unroll
+          for (int j = 0; j < SCAN_DREG / 4; ++j) {
+            const int i = 4 * j;
+            k4[j] = *reinterpret_cast<const float4*>(k + (j * RSPLIT + part) * 4);
+            S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
+            d0 = fmaf(S[i], k4[j].x, d0); d1 = fmaf(S[i + 1], k4[j].y, d1);
+            d2 = fmaf(S[i + 2], k4[j].z, d2); d3 = fmaf(S[i + 3], k4[j].w, d3);
+          }
+          float dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
+          for (int m = 1; m < RSPLIT; m <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
+          const float u = beta * (v - dot);
+#pragma unroll
+          for (int j = 0; j < SCAN_DREG / 4; ++j) {
+            const int i = 4 * j;
+            const float4 q4 = *reinterpret_cast<const float4*>(q + (j * RSPLIT + part) * 4);
+            S[i] = fmaf(k4[j].x, u, S[i]);         o0 = fmaf(S[i], q4.x, o0);
+            S[i + 1] = fmaf(k4[j].y, u, S[i + 1]); o1 = fmaf(S[i + 1], q4.y, o1);
+            S[i + 2] = fmaf(k4[j].z, u, S[i + 2]); o2 = fmaf(S[i + 2], q4.z, o2);
+            S[i + 3] = fmaf(k4[j].w, u, S[i + 3]); o3 = fmaf(S[i + 3], q4.w, o3);
+          }
+        }
+        float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+        for (int m = 1; m < RSPLIT; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
+        if (live && part == 0) p.out[((size_t)(t0 + tt) * p.heads + h) * V + col] = o;
+      }
+    }
+    if (next < end) store_values(stage ^ 1);
+    scan_copies_done();
+    __syncthreads();
   }
   if (live)
 #pragma unroll
-    for (int i = 0; i < DREG; ++i)
-      if (row0 + i < D) S_global[(size_t)(row0 + i) * V + col] = S[i];
+    for (int i = 0; i < SCAN_DREG; ++i) {
+      const int row = ((i >> 2) * RSPLIT + part) * 4 + (i & 3);
+      if (row < D) S_global[(size_t)row * V + col] = S[i];
+    }
 }
 
-template <typename TIN, int MODE>
+template <typename TV, int MODE>
 static int launch_state_scan(const ScanParams& p_in, int num_reqs, cudaStream_t stream) {
   ScanParams p = p_in;
-  const int D = p.D, V = p.V;
-  int dreg = 16, rsplit = 1;
-  while (dreg < D && dreg < 128) dreg *= 2;
-  while (dreg * rsplit < D) rsplit *= 2;
-  KVB_REQUIRE(rsplit <= 4, "state_scan: keys wider than 512 entries");
-  const int dp = dreg * rsplit;
-  // columns a block: all of the head's up to the thread limit, in whole warps
-  int cols = ((V + 31) / 32) * 32;
-  if (cols * rsplit > SCAN_MAX_THREADS) cols = SCAN_MAX_THREADS / rsplit;
-  const int chunks = (V + cols - 1) / cols;
-  const size_t per_token = ((size_t)dp * (MODE == 0 ? 3 : 2) + (MODE == 0 ? 0 : 2) + cols) * sizeof(float);
-  int batch = (int)((40 * 1024) / per_token);
-  batch = batch < 1 ? 1 : batch > 32 ? 32 : batch;
-  p.batch = batch;
-  const size_t smem = per_token * batch;
-  const dim3 grid(num_reqs, p.heads, chunks), block(cols * rsplit);
+  // the split of a column depends on the key width alone, so every cut of a request sums in the same order
+  int rsplit = 1;
+  while (SCAN_DREG * rsplit < p.D) rsplit *= 2;
+  KVB_REQUIRE(rsplit <= 32, "state_scan: keys wider than 512 entries");
+  p.vec16 = (p.D % 4 == 0 && p.vec_token % 4 == 0 && ((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.a) % 16 == 0) ? 1 : 0;
+  const int cols = SCAN_THREADS / rsplit;
+  const dim3 grid(num_reqs, p.heads, (p.V + cols - 1) / cols), block(SCAN_THREADS);
   cudaError_t err = cudaErrorInvalidValue;
-#define SCAN_CASE(DR, RS)                                                                                     \
-  if (dreg == DR && rsplit == RS)                                                                             \
-    err = kvb_launch((state_scan_kernel<TIN, MODE, DR, RS>), grid, block, smem, stream, true, p)
-  SCAN_CASE(16, 1); SCAN_CASE(32, 1); SCAN_CASE(64, 1); SCAN_CASE(128, 1); SCAN_CASE(128, 2); SCAN_CASE(128, 4);
+#define SCAN_CASE(RS, B)                                                                                      \
+  if (rsplit == RS) {                                                                                         \
+    const size_t smem = 2 * (size_t)B * ((MODE == 0 ? 3 : 2) * SCAN_DREG * RS + 4 + SCAN_THREADS / RS) * sizeof(float); \
+    err = kvb_launch((state_scan_kernel<TV, MODE, RS, B>), grid, block, smem, stream, true, p);               \
+  }
+  SCAN_CASE(1, 8) SCAN_CASE(2, 8) SCAN_CASE(4, 8) SCAN_CASE(8, 8) SCAN_CASE(16, 4) SCAN_CASE(32, 2)
 #undef SCAN_CASE
   KVB_CHECK_CUDA(err);
   KVB_CHECK_LAUNCH();
   return 0;
 }
 
+// What the decay-per-channel scan reads, 32-bit [T, 3 * H * D]: q times q_scale, k, and the decays
+// a = sigmoid(z)^(1/tau) = exp(log_sigmoid(z) / tau) with log_sigmoid(z) = min(z, 0) - log1p(exp(-|z|)).
+template <typename T>
+__global__ void __launch_bounds__(256)
+gla_prepare_kernel(float* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k, long long row_stride,
+                   const T* __restrict__ z, long long z_stride, long long tokens, int width, float q_scale,
+                   float inv_tau) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_GLA_PREPARE);
+  const long long total = tokens * width;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const long long t = e / width;
+    const int i = (int)(e - t * width);
+    float* row = out + t * 3 * width;
+    const float zv = to_float(z[t * z_stride + i]);
+    row[i] = to_float(q[t * row_stride + i]) * q_scale;
+    row[width + i] = to_float(k[t * row_stride + i]);
+    row[2 * width + i] = expf((fminf(zv, 0.0f) - log1pf(expf(-fabsf(zv)))) * inv_tau);
+  }
+}
+
 // Decay per key channel.  q, k, v: columns of the projected rows (row stride `row_stride`, heads side by side);
-// z [T, H * D] (row stride z_stride): the decay's logits.
-extern "C" int kvb_gla_scan(float* out, const void* q, const void* k, const void* v, long long row_stride,
-                            const void* z, long long z_stride, float* state, long long state_stride,
-                            long long state_offset, const int* query_start, const int* state_slots, int num_reqs,
-                            int heads, int D, int V, float q_scale, float tau, int dtype, cudaStream_t stream) {
-  if (num_reqs == 0) return 0;
+// z [T, H * D] (row stride z_stride): the decay's logits; prepared: scratch, 32-bit [T, 3 * H * D].
+extern "C" int kvb_gla_scan(float* out, float* prepared, const void* q, const void* k, const void* v,
+                            long long row_stride, const void* z, long long z_stride, float* state,
+                            long long state_stride, long long state_offset, const int* query_start,
+                            const int* state_slots, int tokens, int num_reqs, int heads, int D, int V, float q_scale,
+                            float tau, int dtype, cudaStream_t stream) {
+  if (num_reqs == 0 || tokens == 0) return 0;
   KVB_REQUIRE(heads > 0 && D > 0 && V > 0 && tau > 0.0f, "gla_scan: bad sizes");
-  KVB_REQUIRE(heads <= 65535 && num_reqs > 0, "gla_scan: too many heads");
+  KVB_REQUIRE(heads <= 65535, "gla_scan: too many heads");
+  const int width = heads * D;
+  const long long wanted = ((long long)tokens * width + 255) / 256;
+  const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
+  const dim3 grid((unsigned)(wanted < resident ? wanted : resident));
+  if (dtype == KVB_F32)
+    KVB_CHECK_CUDA(kvb_launch((gla_prepare_kernel<float>), grid, dim3(256), 0, stream, true, prepared, (const float*)q,
+        (const float*)k, row_stride, (const float*)z, z_stride, (long long)tokens, width, q_scale, 1.0f / tau));
+  else
+    KVB_CHECK_CUDA(kvb_launch((gla_prepare_kernel<bf16>), grid, dim3(256), 0, stream, true, prepared, (const bf16*)q,
+        (const bf16*)k, row_stride, (const bf16*)z, z_stride, (long long)tokens, width, q_scale, 1.0f / tau));
   ScanParams p = {};
-  p.q = q; p.k = k; p.v = v; p.z = z;
-  p.q_token = p.k_token = p.v_token = row_stride; p.q_head = p.k_head = D; p.v_head = V;
-  p.z_token = z_stride; p.z_head = D;
+  p.q = prepared; p.k = prepared + width; p.a = prepared + 2 * width; p.vec_token = 3LL * width;
+  p.v = v; p.v_token = row_stride;
   p.out = out; p.state = state; p.state_stride = state_stride; p.state_offset = state_offset;
   p.query_start = query_start; p.state_slots = state_slots;
-  p.heads = heads; p.kv_share = 1; p.D = D; p.V = V; p.q_scale = q_scale; p.inv_tau = 1.0f / tau;
+  p.heads = heads; p.kv_share = 1; p.D = D; p.V = V;
   return dtype == KVB_F32 ? launch_state_scan<float, 0>(p, num_reqs, stream) : launch_state_scan<bf16, 0>(p, num_reqs, stream);
 }
 
@@ -212,11 +299,11 @@ extern "C" int kvb_delta_scan(float* out, const float* prepared, float* state, l
   KVB_REQUIRE(heads <= 65535, "delta_scan: too many heads");
   const long long width = 2LL * kv_heads * D + (long long)heads * V + 2LL * heads;
   ScanParams p = {};
-  p.q = prepared; p.k = prepared + (size_t)kv_heads * D; p.v = prepared + 2 * (size_t)kv_heads * D;
-  p.q_token = p.k_token = p.v_token = width; p.q_head = p.k_head = D; p.v_head = V;
+  p.q = prepared; p.k = prepared + (size_t)kv_heads * D; p.a = prepared; p.vec_token = width;
+  p.v = prepared + 2 * (size_t)kv_heads * D; p.v_token = width;
   p.out = out; p.state = state; p.state_stride = state_stride; p.state_offset = state_offset;
   p.query_start = query_start; p.state_slots = state_slots;
-  p.heads = heads; p.kv_share = heads / kv_heads; p.D = D; p.V = V; p.q_scale = 1.0f; p.inv_tau = 0.0f;
+  p.heads = heads; p.kv_share = heads / kv_heads; p.D = D; p.V = V;
   p.beta = prepared + 2 * (size_t)kv_heads * D + (size_t)heads * V;
   p.gate = p.beta + heads;
   p.bg_stride = width;

@@ -87,8 +87,8 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_sigmoid_gate_mul": [_vp, _vp, _ll, _ll, _vp, _ll, _int, _int, _int, _int, _vp],
         "kvb_gemm_stream_bf16": [_vp, _int, _ll, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _vp, _int, _float, _vp,
                                  _int, _vp, _vp, _vp, _int, _vp],
-        "kvb_gla_scan": [_vp, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _float,
-                         _float, _int, _vp],
+        "kvb_gla_scan": [_vp, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _int,
+                         _float, _float, _int, _vp],
         "kvb_delta_scan": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _int, _vp],
         "kvb_conv_prepare": [_vp, _vp, _ll, _vp, _int, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int,
                              _int, _int, _int, _int, _float, _float, _int, _vp],
@@ -669,7 +669,7 @@ _stream_scratch: dict[int, torch.Tensor] = {}
 TRACE_TAGS = {27: "rms_norm_shift", 28: "stream_add_norm", 29: "attention_dims_rows", 30: "latent_prepare",
               31: "head_norm_kv_write", 32: "maps_combine", 33: "sigmoid_gate_mul", 34: "flash_dims",
               35: "flash_dims_combine", 36: "gather_cached_rows", 37: "gla_scan", 38: "delta_scan", 39: "conv_prepare",
-              40: "gated_rms_norm", 41: "turn_norm_kv_write", 42: "head_gate", 43: "embed_scaled", 25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
+              40: "gated_rms_norm", 41: "turn_norm_kv_write", 42: "head_gate", 43: "embed_scaled", 44: "gla_prepare", 25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
               22: "moe_align", 23: "moe_gemm", 24: "moe_combine", 1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
               11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
@@ -1396,10 +1396,12 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
         raise KernelError("gla_scan: widths do not match the head layout")
     _state_row(state, state_offset, heads * dim * value_dim)
     out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
-    _call("kvb_gla_scan", out.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), z.data_ptr(),
-          z.stride(0), state.data_ptr(), state.stride(0), state_offset, ctx.query_start.data_ptr(),
-          ctx.state_slots.data_ptr(), ctx.num_reqs, heads, dim, value_dim, float(q_scale), float(tau), _dtype_code(q),
-          _stream())
+    # what the scan reads a token, 32-bit: q times its scale, k, the decays
+    prepared = torch.empty((q.shape[0], 3 * heads * dim), dtype=torch.float32, device=q.device)
+    _call("kvb_gla_scan", out.data_ptr(), prepared.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0),
+          z.data_ptr(), z.stride(0), state.data_ptr(), state.stride(0), state_offset, ctx.query_start.data_ptr(),
+          ctx.state_slots.data_ptr(), q.shape[0], ctx.num_reqs, heads, dim, value_dim, float(q_scale), float(tau),
+          _dtype_code(q), _stream())
     return out
 
 
