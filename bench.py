@@ -658,7 +658,7 @@ def dutivik_config(size: dict, kinds: str) -> dict:
     for kind in (kinds * DESIGN_LAYERS)[:DESIGN_LAYERS]:
         if kind == "g":
             layers.append({"type": "gla", "mlp": {"kind": "dense", "ff": size["ff"]},
-                           "mixer": {"heads": half, "dim": dim, "vdim": 2 * dim, "tau": 16.0, "decay_rank": 16}})
+                           "mixer": {"heads": half, "dim": dim, "vdim": 2 * dim, "tau": 8.0, "decay_rank": 16}})
             continue
         left = {"heads": half, "kv_heads": kv_half, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
                 "mask": {"size": 1024}, "rot": {"base": 10000.0, "dims": dim // 2, "scaling": {"factor": 4.0}}}

@@ -13,7 +13,7 @@ import torch
 
 
 # ---- configurations and weights of the tests --------------------------------------------------------
-def gla_layer(*, heads, dim, vdim, tau=16.0, rank=8, ff=48, weights_of=None):
+def gla_layer(*, heads, dim, vdim, tau=4.0, rank=8, ff=48, weights_of=None):
     layer = dict(type="gla", mixer=dict(heads=heads, dim=dim, vdim=vdim, tau=tau),
                  mlp=None if ff is None else dict(kind="dense", ff=ff))
     layer["_rank"] = rank          # the low-rank size of the decay projection is a tensor's shape, not a key

@@ -76,11 +76,11 @@ CONFIGS = {
     # sizes the tensor-core attention takes (widths in steps of 16), windows across several pages, key sizes that
     # fill the state kernel's registers and ones that are shared by two threads a column
     "serving_sizes": P.model_config([
-        S(heads=4, kv_heads=1, dim=64, vdim=128, window=40, rot_dims=32, base=250000.0, factor=4.0,
+        S(heads=4, kv_heads=1, dim=64, vdim=128, window=44, rot_dims=32, base=500000.0, factor=4.0,
           r_heads=4, r_kv_heads=2, r_dim=128, r_vdim=64, conv=4),
-        G(heads=2, dim=192, vdim=32, tau=16.0, rank=16),
+        G(heads=2, dim=192, vdim=32, tau=12.0, rank=16),
         S(heads=4, kv_heads=2, dim=32, vdim=48, window=70, rot_dims=32, base=10000.0,
-          r_heads=2, r_kv_heads=1, r_dim=64, r_vdim=288, conv=3, left_scale=1.2, right_scale=0.9),
+          r_heads=2, r_kv_heads=1, r_dim=64, r_vdim=288, conv=3, left_scale=1.4, right_scale=0.6),
         G(heads=2, dim=192, vdim=32, weights_of=1),
     ], vocab=128, width=64),
 }
