@@ -10,13 +10,16 @@
 //     delta rule with one decay per head:
 //         S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
 //         with q_t, k_t, v_t, beta_t, g_t as `conv_prepare` left them (32-bit).
-//   A column of S is shared by RSPLIT neighbouring lanes (16 rows each, in registers; RSPLIT follows from the
-//   key width alone), a block owns 128 / RSPLIT columns of one (request, head): a single prompt already fills
-//   the machine with H * V * RSPLIT / 128 blocks, and a decode step reads and writes every state once.
-//   Columns never exchange anything and the lanes of a column sum in a fixed order, so any cut of a request
-//   into steps gives the same bits.  The tokens' vectors (32-bit: q, k, and the decays or beta and gate) come
+//   S is kept column by column ([H, V, D] in the state row: a column's D rows lie together).  A column is shared
+//   by RSPLIT neighbouring lanes (4, 8 or 16 rows each, in registers, loaded and stored as 16-byte pieces), a
+//   block owns 128 / RSPLIT columns of one (request, head).  A launch with few columns (a single prompt) takes
+//   few rows a thread and so puts H * V * D / 128 warps on the machine; one with many (a decode step) takes 16
+//   and reads and writes every state once in large pieces.
+//   Columns never exchange anything, and a sum over a column's rows is taken in one fixed order (four rows at a
+//   time, then a tree over those pieces) whatever the rows a thread, so any cut of a request into steps and any
+//   batch it runs in give the same bits.  The tokens' vectors (32-bit: q, k, and the decays or beta and gate) come
 //   through two stages of shared memory by cp.async, a few tokens a stage, the next stage in flight while this
-//   one is computed.  gla_prepare writes those vectors for the decay-per-channel form (q times its scale, k,
+//   one is computed; where each thread's copies come from and go to is worked out once, not once a stage.  gla_prepare writes those vectors for the decay-per-channel form (q times its scale, k,
 //   a = sigmoid(z)^(1/tau)) once a token, so the blocks that share a head do not each take the exponentials.
 //
 //   conv_prepare (delta rule): a short causal convolution over time per channel on the q, k and v
@@ -29,7 +32,6 @@
 #include "common.cuh"
 
 #define SCAN_THREADS 128
-#define SCAN_DREG 16
 
 __device__ __forceinline__ void scan_copy16(float* dst, const float* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
@@ -45,29 +47,32 @@ struct ScanParams {
   const float* q; const float* k; const float* a;
   long long vec_token;
   int vec16;                                // every vector starts on a 16-byte boundary and D is a multiple of 4
+  int state16;                              // so does every column of S in the state rows
   const void* v; long long v_token;         // values [V] of head h at v + t * v_token + h * V (elements)
   const float* beta; const float* gate;     // [T, H] with row stride bg_stride (delta rule)
   long long bg_stride;
   float* out;                               // [T, H, V]
-  float* state;                             // [slots, state_stride]; this mixer's S at state_offset, [H, D, V]
+  float* state;                             // [slots, state_stride]; this mixer's S at state_offset, [H, V, D]
   long long state_stride, state_offset;
   const int* query_start; const int* state_slots;
   int heads, kv_share, D, V;
 };
 
-// MODE 0: decay per key channel; MODE 1: delta rule.  RSPLIT threads a column of S, SCAN_DREG rows each;
+// MODE 0: decay per key channel; MODE 1: delta rule.  RSPLIT threads a column of S, DREG rows each;
 // BATCH tokens a stage of shared memory.
-template <typename TV, int MODE, int RSPLIT, int BATCH>
+template <typename TV, int MODE, int DREG, int RSPLIT, int BATCH>
 __global__ void __launch_bounds__(SCAN_THREADS)
 state_scan_kernel(ScanParams p) {
   KVB_KERNEL_PROLOGUE(MODE == 0 ? KVB_TAG_GLA_SCAN : KVB_TAG_DELTA_SCAN);
   extern __shared__ __align__(16) float smem[];
-  constexpr int DP = SCAN_DREG * RSPLIT;            // rows covered (>= D; rows beyond D stay zero)
+  constexpr int DP = DREG * RSPLIT;                 // rows covered (>= D; rows beyond D stay zero)
   constexpr int COLS = SCAN_THREADS / RSPLIT;       // columns this block owns
   constexpr int NVEC = MODE == 0 ? 3 : 2;           // q, k (, a)
   constexpr int TOKEN = NVEC * DP + 4;              // floats a token holds in a stage; the last four: beta, gate
   constexpr int STAGE = BATCH * TOKEN;
   constexpr int VPT = (BATCH * COLS + SCAN_THREADS - 1) / SCAN_THREADS;
+  constexpr int FPT = (BATCH * NVEC * (DP / 4) + SCAN_THREADS - 1) / SCAN_THREADS;   // 16-byte copies a thread, a stage
+  constexpr int J = DREG / 4;
   float* const vectors = smem;                      // [2][BATCH][TOKEN]
   float* const values = smem + 2 * STAGE;           // [2][BATCH][COLS]
 
@@ -80,37 +85,63 @@ state_scan_kernel(ScanParams p) {
   const int kvh = h / p.kv_share;
   const TV* vg = (const TV*)p.v;
 
-  // Thread `part` of a column holds rows (j * RSPLIT + part) * 4 + m, j and m in 0..3: for one j the parts of a
-  // column read neighbouring 16-byte pieces of a vector.
-  float* S_global = p.state + (size_t)p.state_slots[req] * p.state_stride + p.state_offset + (size_t)h * D * V;
-  float S[SCAN_DREG];
+  // Thread `part` of a column holds the column's rows part * DREG .. part * DREG + DREG - 1 as J 16-byte pieces.
+  // In shared memory a vector's piece n lies at place (n % J) * RSPLIT + n / J, so that for one j the parts of a
+  // column read neighbouring pieces.
+  float* S_column = p.state + (size_t)p.state_slots[req] * p.state_stride + p.state_offset +
+                    ((size_t)h * V + (live ? col : 0)) * D;
+  float S[DREG];
 #pragma unroll
-  for (int i = 0; i < SCAN_DREG; ++i) {
-    const int row = ((i >> 2) * RSPLIT + part) * 4 + (i & 3);
-    S[i] = (live && row < D) ? S_global[(size_t)row * V + col] : 0.0f;
+  for (int j = 0; j < J; ++j) {
+    const int row = part * DREG + 4 * j;
+    float4 s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (live && row < D) {
+      if (p.state16) {
+        s4 = *reinterpret_cast<const float4*>(S_column + row);
+      } else {
+        s4.x = S_column[row];
+        if (row + 1 < D) s4.y = S_column[row + 1];
+        if (row + 2 < D) s4.z = S_column[row + 2];
+        if (row + 3 < D) s4.w = S_column[row + 3];
+      }
+    }
+    S[4 * j] = s4.x; S[4 * j + 1] = s4.y; S[4 * j + 2] = s4.z; S[4 * j + 3] = s4.w;
   }
+  auto place = [](int row) { return (((row >> 2) % J) * RSPLIT + (row >> 2) / J) * 4 + (row & 3); };
   if (D < DP)                                       // rows beyond D read zeros whatever the stage holds
     for (int e = tid; e < 2 * BATCH * NVEC * (DP - D); e += SCAN_THREADS) {
       const int slot = e / (DP - D), i = D + e % (DP - D);
-      vectors[(slot / NVEC) * TOKEN + (slot % NVEC) * DP + i] = 0.0f;
+      vectors[(slot / NVEC) * TOKEN + (slot % NVEC) * DP + place(i)] = 0.0f;
     }
 
+  // Where this thread's 16-byte copies of a stage come from (for the stage that starts at token 0) and go to:
+  // the same for every stage, so the divisions are taken once.
+  const float* copy_from[FPT];
+  int copy_to[FPT];
+  const int pieces = D >> 2, per_token = NVEC * pieces;
+  if (p.vec16) {
+#pragma unroll
+    for (int n = 0; n < FPT; ++n) {
+      const int e = tid + n * SCAN_THREADS;
+      const int tt = e / per_token, r = e - tt * per_token, vec = r / pieces, i = (r - vec * pieces) << 2;
+      const float* base = vec == 0 ? p.q : vec == 1 ? p.k : p.a;
+      copy_from[n] = base + (long long)tt * p.vec_token + (long long)(vec == 2 ? h : kvh) * D + i;
+      copy_to[n] = tt * TOKEN + vec * DP + place(i);
+    }
+  }
   auto fetch = [&](int stage, int t0, int nb) {     // the vectors of tokens t0 .. t0 + nb - 1, asynchronously
     float* dst = vectors + stage * STAGE;
     if (p.vec16) {
-      const int pieces = D >> 2, per_token = NVEC * pieces;
-      for (int e = tid; e < nb * per_token; e += SCAN_THREADS) {
-        const int tt = e / per_token, r = e - tt * per_token, vec = r / pieces, i = (r - vec * pieces) << 2;
-        const float* base = vec == 0 ? p.q : vec == 1 ? p.k : p.a;
-        scan_copy16(dst + tt * TOKEN + vec * DP + i,
-                    base + (long long)(t0 + tt) * p.vec_token + (long long)(vec == 2 ? h : kvh) * D + i);
-      }
+      const long long shift = (long long)t0 * p.vec_token;
+#pragma unroll
+      for (int n = 0; n < FPT; ++n)
+        if (tid + n * SCAN_THREADS < nb * per_token) scan_copy16(dst + copy_to[n], copy_from[n] + shift);
     } else {
-      const int per_token = NVEC * D;
-      for (int e = tid; e < nb * per_token; e += SCAN_THREADS) {
-        const int tt = e / per_token, r = e - tt * per_token, vec = r / D, i = r - vec * D;
+      const int floats = NVEC * D;
+      for (int e = tid; e < nb * floats; e += SCAN_THREADS) {
+        const int tt = e / floats, r = e - tt * floats, vec = r / D, i = r - vec * D;
         const float* base = vec == 0 ? p.q : vec == 1 ? p.k : p.a;
-        scan_copy4(dst + tt * TOKEN + vec * DP + i,
+        scan_copy4(dst + tt * TOKEN + vec * DP + place(i),
                    base + (long long)(t0 + tt) * p.vec_token + (long long)(vec == 2 ? h : kvh) * D + i);
       }
     }
@@ -136,6 +167,61 @@ state_scan_kernel(ScanParams p) {
       if (e < BATCH * COLS) values[stage * BATCH * COLS + e] = held[j];
     }
   };
+  // One token: the state's step and the read-out of this thread's column.  A sum over a column's rows is taken
+  // piece by piece (four rows, in order), and the pieces are added as a tree over their numbers (n with n ^ 1,
+  // then with n ^ 2, ...): inside a thread for the pieces it holds, by shuffles between the threads of a column.
+  // The result has the same bits for every DREG, so a launch may pick DREG by how many columns it has.
+  auto tree = [&](float (&piece)[J]) {
+    float sum = piece[0];
+    if constexpr (J == 2) sum = piece[0] + piece[1];
+    if constexpr (J == 4) sum = (piece[0] + piece[1]) + (piece[2] + piece[3]);
+#pragma unroll
+    for (int m = 1; m < RSPLIT; m <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+    return sum;
+  };
+  auto token = [&](const float* q, float v, float* out_at) {
+    const float* k = q + DP;
+    float o[J];
+    if (MODE == 0) {
+      const float* a = k + DP;
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        const int at = (j * RSPLIT + part) * 4, i = 4 * j;
+        const float4 a4 = *reinterpret_cast<const float4*>(a + at);
+        const float4 k4 = *reinterpret_cast<const float4*>(k + at);
+        const float4 q4 = *reinterpret_cast<const float4*>(q + at);
+        S[i] = fmaf(k4.x, v, a4.x * S[i]);
+        S[i + 1] = fmaf(k4.y, v, a4.y * S[i + 1]);
+        S[i + 2] = fmaf(k4.z, v, a4.z * S[i + 2]);
+        S[i + 3] = fmaf(k4.w, v, a4.w * S[i + 3]);
+        o[j] = fmaf(S[i + 3], q4.w, fmaf(S[i + 2], q4.z, fmaf(S[i + 1], q4.y, S[i] * q4.x)));
+      }
+    } else {
+      const float beta = q[NVEC * DP], g = q[NVEC * DP + 1];
+      float4 k4[J];
+      float d[J];
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        const int i = 4 * j;
+        k4[j] = *reinterpret_cast<const float4*>(k + (j * RSPLIT + part) * 4);
+        S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
+        d[j] = fmaf(S[i + 3], k4[j].w, fmaf(S[i + 2], k4[j].z, fmaf(S[i + 1], k4[j].y, S[i] * k4[j].x)));
+      }
+      const float u = beta * (v - tree(d));
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        const int i = 4 * j;
+        const float4 q4 = *reinterpret_cast<const float4*>(q + (j * RSPLIT + part) * 4);
+        S[i] = fmaf(k4[j].x, u, S[i]);
+        S[i + 1] = fmaf(k4[j].y, u, S[i + 1]);
+        S[i + 2] = fmaf(k4[j].z, u, S[i + 2]);
+        S[i + 3] = fmaf(k4[j].w, u, S[i + 3]);
+        o[j] = fmaf(S[i + 3], q4.w, fmaf(S[i + 2], q4.z, fmaf(S[i + 1], q4.y, S[i] * q4.x)));
+      }
+    }
+    const float sum = tree(o);
+    if (live && part == 0) *out_at = sum;
+  };
 
   if (begin < end) {
     fetch(0, begin, min(BATCH, end - begin));
@@ -145,6 +231,7 @@ state_scan_kernel(ScanParams p) {
   scan_copies_done();
   __syncthreads();
   int stage = 0;
+  const size_t out_token = (size_t)p.heads * V;
   for (int t0 = begin; t0 < end; t0 += BATCH, stage ^= 1) {
     const int nb = min(BATCH, end - t0);
     const int next = t0 + BATCH, next_nb = min(BATCH, end - next);
@@ -153,58 +240,13 @@ state_scan_kernel(ScanParams p) {
       load_values(next, next_nb);
     }
     const float* st = vectors + stage * STAGE;
-    const float* vs = values + stage * BATCH * COLS;
+    const float* vs = values + stage * BATCH * COLS + c;
+    float* out_at = p.out + ((size_t)t0 * p.heads + h) * V + (live ? col : 0);
+    if (nb == BATCH) {                                // a full stage: nothing to ask between its tokens
 #pragma unroll
-    for (int tt = 0; tt < BATCH; ++tt) {
-      if (tt < nb) {
-        const float* q = st + tt * TOKEN;
-        const float* k = q + DP;
-        const float v = vs[tt * COLS + c];
-        float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
-        if (MODE == 0) {
-          const float* a = k + DP;
-#pragma unroll
-          for (int j = 0; j < SCAN_DREG / 4; ++j) {
-            const int at = (j * RSPLIT + part) * 4, i = 4 * j;
-            const float4 a4 = *reinterpret_cast<const float4*>(a + at);
-            const float4 k4 = *reinterpret_cast<const float4*>(k + at);
-            const float4 q4 = *reinterpret_cast<const float4*>(q + at);
-            S[i] = fmaf(k4.x, v, a4.x * S[i]);         o0 = fmaf(S[i], q4.x, o0);
-            S[i + 1] = fmaf(k4.y, v, a4.y * S[i + 1]); o1 = fmaf(S[i + 1], q4.y, o1);
-            S[i + 2] = fmaf(k4.z, v, a4.z * S[i + 2]); o2 = fmaf(S[i + 2], q4.z, o2);
-            S[i + 3] = fmaf(k4.w, v, a4.w * S[i + 3]); o3 = fmaf(S[i + 3], q4.w, o3);
-          }
-        } else {
-          const float beta = q[NVEC * DP], g = q[NVEC * DP + 1];
-          float4 k4[SCAN_DREG / 4];
-          float d0 = 0.0f, d1 = 0.0f, d2 = 0.0f, d3 = 0.0f;
-#pragma unroll
-          for (int j = 0; j < SCAN_DREG / 4; ++j) {
-            const int i = 4 * j;
-            k4[j] = *reinterpret_cast<const float4*>(k + (j * RSPLIT + part) * 4);
-            S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
-            d0 = fmaf(S[i], k4[j].x, d0); d1 = fmaf(S[i + 1], k4[j].y, d1);
-            d2 = fmaf(S[i + 2], k4[j].z, d2); d3 = fmaf(S[i + 3], k4[j].w, d3);
-          }
-          float dot = (d0 + d1) + (d2 + d3);
-#pragma unroll
-          for (int m = 1; m < RSPLIT; m <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
-          const float u = beta * (v - dot);
-#pragma unroll
-          for (int j = 0; j < SCAN_DREG / 4; ++j) {
-            const int i = 4 * j;
-            const float4 q4 = *reinterpret_cast<const float4*>(q + (j * RSPLIT + part) * 4);
-            S[i] = fmaf(k4[j].x, u, S[i]);         o0 = fmaf(S[i], q4.x, o0);
-            S[i + 1] = fmaf(k4[j].y, u, S[i + 1]); o1 = fmaf(S[i + 1], q4.y, o1);
-            S[i + 2] = fmaf(k4[j].z, u, S[i + 2]); o2 = fmaf(S[i + 2], q4.z, o2);
-            S[i + 3] = fmaf(k4[j].w, u, S[i + 3]); o3 = fmaf(S[i + 3], q4.w, o3);
-          }
-        }
-        float o = (o0 + o1) + (o2 + o3);
-#pragma unroll
-        for (int m = 1; m < RSPLIT; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
-        if (live && part == 0) p.out[((size_t)(t0 + tt) * p.heads + h) * V + col] = o;
-      }
+      for (int tt = 0; tt < BATCH; ++tt) token(st + tt * TOKEN, vs[tt * COLS], out_at + tt * out_token);
+    } else {
+      for (int tt = 0; tt < nb; ++tt) token(st + tt * TOKEN, vs[tt * COLS], out_at + tt * out_token);
     }
     if (next < end) store_values(stage ^ 1);
     scan_copies_done();
@@ -212,29 +254,63 @@ state_scan_kernel(ScanParams p) {
   }
   if (live)
 #pragma unroll
-    for (int i = 0; i < SCAN_DREG; ++i) {
-      const int row = ((i >> 2) * RSPLIT + part) * 4 + (i & 3);
-      if (row < D) S_global[(size_t)row * V + col] = S[i];
+    for (int j = 0; j < J; ++j) {
+      const int row = part * DREG + 4 * j;
+      if (row < D) {
+        if (p.state16) {
+          *reinterpret_cast<float4*>(S_column + row) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+        } else {
+          S_column[row] = S[4 * j];
+          if (row + 1 < D) S_column[row + 1] = S[4 * j + 1];
+          if (row + 2 < D) S_column[row + 2] = S[4 * j + 2];
+          if (row + 3 < D) S_column[row + 3] = S[4 * j + 3];
+        }
+      }
     }
+}
+
+// Rows of S a thread holds.  Sums over a column come out with the same bits whatever the choice, so it follows
+// the launch: 16 rows a thread when that already gives every SM three blocks (many requests, or a decode step,
+// where each block then moves 8 KB of state and more), else 8, else 4 (a single prompt has only H * V columns to
+// offer, and one token's step is a chain of dependent instructions that only more warps can hide).
+static int scan_rows_per_thread(int D, long long columns_of_all_heads, int V) {
+  const long long wanted = 3LL * (kvb_sm_count() > 0 ? kvb_sm_count() : 148);
+  const char* asked = getenv("KVCORE_SCAN_ROWS");     // tests run every choice on one input and compare the bits
+  const int most = asked && (atoi(asked) == 4 || atoi(asked) == 8) ? atoi(asked) : 16;
+  const bool forced = asked && atoi(asked) == most;
+  for (int rows = most; rows > 4; rows >>= 1) {
+    int rsplit = 1;
+    while (rows * rsplit < D) rsplit *= 2;
+    const int cols = SCAN_THREADS / rsplit;
+    if (rows * 32 < D) break;
+    if (forced || columns_of_all_heads / V * ((V + cols - 1) / cols) >= wanted) return rows;
+  }
+  int rows = 4;
+  while (rows * 32 < D) rows *= 2;
+  return rows;
 }
 
 template <typename TV, int MODE>
 static int launch_state_scan(const ScanParams& p_in, int num_reqs, cudaStream_t stream) {
   ScanParams p = p_in;
-  // the split of a column depends on the key width alone, so every cut of a request sums in the same order
+  KVB_REQUIRE(p.D <= 512, "state_scan: keys wider than 512 entries");
+  const int dreg = scan_rows_per_thread(p.D, (long long)num_reqs * p.heads * p.V, p.V);
   int rsplit = 1;
-  while (SCAN_DREG * rsplit < p.D) rsplit *= 2;
-  KVB_REQUIRE(rsplit <= 32, "state_scan: keys wider than 512 entries");
+  while (dreg * rsplit < p.D) rsplit *= 2;
   p.vec16 = (p.D % 4 == 0 && p.vec_token % 4 == 0 && ((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.a) % 16 == 0) ? 1 : 0;
+  p.state16 = (p.D % 4 == 0 && p.state_stride % 4 == 0 && p.state_offset % 4 == 0 && (uintptr_t)p.state % 16 == 0) ? 1 : 0;
   const int cols = SCAN_THREADS / rsplit;
   const dim3 grid(num_reqs, p.heads, (p.V + cols - 1) / cols), block(SCAN_THREADS);
   cudaError_t err = cudaErrorInvalidValue;
-#define SCAN_CASE(RS, B)                                                                                      \
-  if (rsplit == RS) {                                                                                         \
-    const size_t smem = 2 * (size_t)B * ((MODE == 0 ? 3 : 2) * SCAN_DREG * RS + 4 + SCAN_THREADS / RS) * sizeof(float); \
-    err = kvb_launch((state_scan_kernel<TV, MODE, RS, B>), grid, block, smem, stream, true, p);               \
+#define SCAN_CASE(DR, RS)                                                                                     \
+  if (dreg == DR && rsplit == RS) {                                                                           \
+    constexpr int B = DR * RS <= 128 ? 8 : 1024 / (DR * RS);                                                  \
+    const size_t smem = 2 * (size_t)B * ((MODE == 0 ? 3 : 2) * DR * RS + 4 + SCAN_THREADS / RS) * sizeof(float); \
+    err = kvb_launch((state_scan_kernel<TV, MODE, DR, RS, B>), grid, block, smem, stream, true, p);           \
   }
-  SCAN_CASE(1, 8) SCAN_CASE(2, 8) SCAN_CASE(4, 8) SCAN_CASE(8, 8) SCAN_CASE(16, 4) SCAN_CASE(32, 2)
+  SCAN_CASE(4, 1) SCAN_CASE(4, 2) SCAN_CASE(4, 4) SCAN_CASE(4, 8) SCAN_CASE(4, 16) SCAN_CASE(4, 32)
+  SCAN_CASE(8, 1) SCAN_CASE(8, 2) SCAN_CASE(8, 4) SCAN_CASE(8, 8) SCAN_CASE(8, 16) SCAN_CASE(8, 32)
+  SCAN_CASE(16, 1) SCAN_CASE(16, 2) SCAN_CASE(16, 4) SCAN_CASE(16, 8) SCAN_CASE(16, 16) SCAN_CASE(16, 32)
 #undef SCAN_CASE
   KVB_CHECK_CUDA(err);
   KVB_CHECK_LAUNCH();

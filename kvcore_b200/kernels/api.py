@@ -1384,7 +1384,8 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     ``S <- diag(a_t) S + k_t v_t^T``, ``o_t = S^T (q_t * q_scale)`` with ``a_t = sigmoid(z_t)^(1/tau)``.
     ``q, k [T, heads * dim]`` and ``v [T, heads * value_dim]`` are views of one tensor of projected rows,
     ``z [T, heads * dim]`` the decay's logits; ``state [slots, n]`` (32-bit) holds each request's
-    ``S [heads, dim, value_dim]`` at ``state_offset`` of its slot's row and is brought up to date.
+    ``S`` column by column (``[heads, value_dim, dim]``) at ``state_offset`` of its slot's row and is brought up
+    to date.
     Returns ``o [T, heads, value_dim]`` 32-bit."""
     for name, t in (("q", q), ("k", k), ("v", v), ("z", z)):
         _check(t, name, dtype=q.dtype, contiguous=False)
@@ -1439,8 +1440,8 @@ def delta_scan(prepared: torch.Tensor, state: torch.Tensor, ctx, *, heads: int, 
                value_dim: int, state_offset: int = 0) -> torch.Tensor:
     """The gated delta rule over the step's tokens, request by request in order, on what ``conv_prepare`` left:
     ``S <- g_t S``; ``u = beta_t (v_t - S^T k_t)``; ``S <- S + k_t u^T``; ``o_t = S^T q_t`` (head ``h`` reads
-    q/k head ``h // (heads / kv_heads)``).  ``state [slots, n]`` holds ``S [heads, dim, value_dim]`` at
-    ``state_offset``.  Returns ``o [T, heads, value_dim]`` 32-bit."""
+    q/k head ``h // (heads / kv_heads)``).  ``state [slots, n]`` holds ``S`` column by column
+    (``[heads, value_dim, dim]``) at ``state_offset``.  Returns ``o [T, heads, value_dim]`` 32-bit."""
     _check(prepared, "prepared", dtype=torch.float32)
     if prepared.dim() != 2 or prepared.shape[1] != 2 * kv_heads * dim + heads * value_dim + 2 * heads:
         raise KernelError(f"delta_scan: prepared rows {tuple(prepared.shape)} do not match the head layout")

@@ -15,7 +15,7 @@ convolution over time and SiLU; q and k become unit vectors (q times ``dim^(-1/2
 ``S <- g S``, ``u = beta (v - S^T k)``, ``S <- S + k u^T``, ``o = S^T q`` with ``beta = sigmoid(W_b x)`` and
 ``g = exp(-exp(A_log) softplus(W_a x + dt_bias))``; ``o`` gets an RMS norm with one weight for all heads and is
 multiplied by ``silu(W_g x)``.  The state of a request is ``S`` and the last ``taps - 1`` inputs of the
-convolution.
+convolution.  Both mixers keep ``S`` column by column (``[heads, value_dim, head_dim]``).
 
 Decays, step sizes, unit norms, the state, the read-out and the norm behind it are 32-bit whatever the
 activation type.
@@ -30,6 +30,12 @@ from .base import MIXERS, Mixer, StateSpec, WeightSlot
 
 def _round8(n: int) -> int:
     return (n + 7) & ~7
+
+
+def _round4(n: int) -> int:
+    """State rows are whole 16-byte pieces, so that every request's (and every member's) state starts on a
+    16-byte boundary and the state kernels move it in such pieces."""
+    return (n + 3) & ~3
 
 
 class ProjectedMixer(Mixer):
@@ -95,7 +101,7 @@ class GatedLinearAttention(ProjectedMixer):
         self.norm_weight = torch.empty(self.value_dim, dtype=dtype, device=device)
 
     def state_spec(self) -> StateSpec:
-        return StateSpec((self.num_heads * self.head_dim * self.value_dim,), torch.float32)
+        return StateSpec((_round4(self.num_heads * self.head_dim * self.value_dim),), torch.float32)
 
     def _tensor(self, key: str) -> str:
         return f"{self.name}.{self.tensor_names[key]}"
@@ -158,7 +164,7 @@ class GatedDeltaRule(ProjectedMixer):
         self.matrix_floats = self.num_heads * self.head_dim * self.value_dim
 
     def state_spec(self) -> StateSpec:
-        return StateSpec((self.matrix_floats + self.channels * (self.conv_taps - 1),), torch.float32)
+        return StateSpec((_round4(self.matrix_floats + self.channels * (self.conv_taps - 1)),), torch.float32)
 
     def _tensor(self, key: str) -> str:
         return f"{self.name}.{self.tensor_names[key]}"

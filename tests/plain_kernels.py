@@ -496,11 +496,11 @@ def gla_scan(q, k, v, z, state, ctx, *, heads, dim, value_dim, q_scale, tau, sta
     qf = q.float().reshape(tokens, heads, dim) * q_scale
     kf, vf = k.float().reshape(tokens, heads, dim), v.float().reshape(tokens, heads, value_dim)
     for _, begin, end, slot in _request_ranges(ctx):
-        S = state[slot, state_offset:state_offset + n].reshape(heads, dim, value_dim).clone()
+        S = state[slot, state_offset:state_offset + n].reshape(heads, value_dim, dim).transpose(1, 2).clone()   # kept column by column
         for t in range(begin, end):
             S = S * alpha[t][:, :, None] + kf[t][:, :, None] * vf[t][:, None, :]
             out[t] = torch.einsum("hdv,hd->hv", S, qf[t])
-        state[slot, state_offset:state_offset + n] = S.reshape(n)
+        state[slot, state_offset:state_offset + n] = S.transpose(1, 2).reshape(n)
     return out
 
 
@@ -541,13 +541,13 @@ def delta_scan(prepared, state, ctx, *, heads, kv_heads, dim, value_dim, state_o
     gate = prepared[:, 2 * qk + heads * value_dim + heads:]
     out = torch.empty((tokens, heads, value_dim), dtype=torch.float32, device=prepared.device)
     for _, begin, end, slot in _request_ranges(ctx):
-        S = state[slot, state_offset:state_offset + n].reshape(heads, dim, value_dim).clone()
+        S = state[slot, state_offset:state_offset + n].reshape(heads, value_dim, dim).transpose(1, 2).clone()   # kept column by column
         for t in range(begin, end):
             S = S * gate[t][:, None, None]
             u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, k[t]))
             S = S + k[t][:, :, None] * u[:, None, :]
             out[t] = torch.einsum("hdv,hd->hv", S, q[t])
-        state[slot, state_offset:state_offset + n] = S.reshape(n)
+        state[slot, state_offset:state_offset + n] = S.transpose(1, 2).reshape(n)
     return out
 
 

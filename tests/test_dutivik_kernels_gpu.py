@@ -35,16 +35,17 @@ class _HostBatch:
         self.num_reqs = batch.num_reqs
 
 
+@pytest.mark.parametrize("front", [3, 8])      # the state begins `front` floats into its row: off and on a 16-byte boundary
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,dim,vdim", SCAN_SIZES)
-def test_decay_per_channel_scan(dtype, heads, dim, vdim):
+def test_decay_per_channel_scan(dtype, heads, dim, vdim, front):
     batch = _Batch(SCAN_LENS, slots=[4, 0, 2, 5])
-    tokens, front = batch.num_tokens, 3                      # the state begins `front` floats into its row
+    tokens = batch.num_tokens
     rows = randn(tokens, 2 * heads * dim + heads * vdim + 8, dtype=dtype, seed=1)
     q, k = rows[:, :heads * dim], rows[:, heads * dim:2 * heads * dim]
     v = rows[:, 2 * heads * dim:2 * heads * dim + heads * vdim]
     z = randn(tokens, heads * dim, dtype=dtype, seed=2, scale=3.0)
-    state, host_state = _states(6, front + heads * dim * vdim + 5, seed=3)
+    state, host_state = _states(6, front + heads * dim * vdim + (5 if front % 4 else 4), seed=3)
     sizes = dict(heads=heads, dim=dim, value_dim=vdim, q_scale=dim ** -0.5, tau=2.5, state_offset=front)
     got = K().gla_scan(q, k, v, z, state, batch, **sizes)
     want = P.gla_scan(q.cpu(), k.cpu(), v.cpu(), z.cpu(), host_state, _HostBatch(batch), **sizes)
@@ -54,7 +55,8 @@ def test_decay_per_channel_scan(dtype, heads, dim, vdim):
 
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 6, 10), (2, 2, 16, 24), (6, 3, 32, 72), (2, 1, 64, 200),
                                                      (4, 1, 128, 40), (1, 1, 200, 20), (2, 2, 256, 12), (2, 1, 512, 8)])
-def test_delta_rule_scan(heads, kv_heads, dim, vdim):
+@pytest.mark.parametrize("front", [7, 4])
+def test_delta_rule_scan(heads, kv_heads, dim, vdim, front):
     batch = _Batch(SCAN_LENS, slots=[1, 3, 0, 2])
     tokens, qk = batch.num_tokens, kv_heads * dim
     prepared = randn(tokens, 2 * qk + heads * vdim + 2 * heads, dtype=torch.float32, seed=4)
@@ -62,8 +64,8 @@ def test_delta_rule_scan(heads, kv_heads, dim, vdim):
     prepared[:, :qk] = unit(prepared[:, :qk]) * dim ** -0.5
     prepared[:, qk:2 * qk] = unit(prepared[:, qk:2 * qk])
     prepared[:, -2 * heads:] = torch.sigmoid(prepared[:, -2 * heads:])          # beta and the decay lie in (0, 1)
-    state, host_state = _states(4, 7 + heads * dim * vdim, seed=5)
-    sizes = dict(heads=heads, kv_heads=kv_heads, dim=dim, value_dim=vdim, state_offset=7)
+    state, host_state = _states(4, front + heads * dim * vdim + (1 if front % 4 else 0), seed=5)
+    sizes = dict(heads=heads, kv_heads=kv_heads, dim=dim, value_dim=vdim, state_offset=front)
     got = K().delta_scan(prepared, state, batch, **sizes)
     want = P.delta_scan(prepared.cpu(), host_state, _HostBatch(batch), **sizes)
     torch.testing.assert_close(got.cpu(), want, **F32)
@@ -104,6 +106,35 @@ def test_scans_do_not_depend_on_the_cut(kind):
         assert not state[:2].any()
 
 
+@pytest.mark.parametrize("dim,vdim", [(40, 24), (128, 40), (200, 12), (512, 8)])
+@pytest.mark.parametrize("kind", ["decay", "delta"])
+def test_scans_do_not_depend_on_the_rows_a_thread_holds(kind, dim, vdim, monkeypatch):
+    """A launch picks how many rows of a column one thread holds by the columns it has (a single prompt, or a
+    batch of many requests): every choice gives the same bits, out and in the state."""
+    heads, kv_heads, lens = 2, 1, [(0, 13), (0, 1), (0, 6)]
+    batch = _Batch(lens, slots=[2, 0, 1])
+    tokens = batch.num_tokens
+    seen = []
+    for rows_a_thread in (None, "4", "8", "16"):
+        if rows_a_thread is None:
+            monkeypatch.delenv("KVCORE_SCAN_ROWS", raising=False)
+        else:
+            monkeypatch.setenv("KVCORE_SCAN_ROWS", rows_a_thread)
+        state, _ = _states(3, heads * dim * vdim, seed=21)
+        if kind == "decay":
+            rows = randn(tokens, 2 * heads * dim + heads * vdim, seed=22, dtype=torch.float32)
+            z = randn(tokens, heads * dim, seed=23, dtype=torch.float32)
+            out = K().gla_scan(rows[:, :heads * dim], rows[:, heads * dim:2 * heads * dim], rows[:, 2 * heads * dim:], z,
+                               state, batch, heads=heads, dim=dim, value_dim=vdim, q_scale=0.3, tau=4.0)
+        else:
+            prepared = randn(tokens, 2 * kv_heads * dim + heads * vdim + 2 * heads, seed=24, dtype=torch.float32) * 0.2
+            prepared[:, -2 * heads:] = torch.sigmoid(prepared[:, -2 * heads:])
+            out = K().delta_scan(prepared, state, batch, heads=heads, kv_heads=kv_heads, dim=dim, value_dim=vdim)
+        seen.append((out.cpu(), state.cpu()))
+    for out, state in seen[1:]:
+        assert torch.equal(out, seen[0][0]) and torch.equal(state, seen[0][1])
+
+
 @pytest.mark.parametrize("kind", ["decay", "delta"])
 def test_a_far_token_is_read_through_the_state(kind):
     """One token writes a value under a key that no other token's key touches; 300 tokens on, with decays of one,
@@ -121,8 +152,9 @@ def test_a_far_token_is_read_through_the_state(kind):
     batch = _Batch([(0, tokens)])
     if kind == "decay":
         z = torch.full((tokens, dim), 40.0)                                  # sigmoid(40) is one in 32-bit
-        out = K().gla_scan(q.to(DEV), k.to(DEV), v.to(DEV), z.to(DEV), state, batch, heads=heads, dim=dim,
-                           value_dim=vdim, q_scale=1.0, tau=1.0)
+        rows = torch.cat([q, k, v], dim=1).to(DEV)                           # q, k and v are views of one tensor of rows
+        out = K().gla_scan(rows[:, :dim], rows[:, dim:2 * dim], rows[:, 2 * dim:], z.to(DEV), state, batch,
+                           heads=heads, dim=dim, value_dim=vdim, q_scale=1.0, tau=1.0)
     else:
         k = k / k.norm(dim=-1, keepdim=True)
         q[:-1] = k[:-1]
