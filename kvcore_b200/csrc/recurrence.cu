@@ -11,16 +11,17 @@
 //         S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
 //         with q_t, k_t, v_t, beta_t, g_t as `conv_prepare` left them (32-bit).
 //   S is kept column by column ([H, V, D] in the state row: a column's D rows lie together).  A column is shared
-//   by RSPLIT neighbouring lanes (4, 8 or 16 rows each, in registers, loaded and stored as 16-byte pieces), a
-//   block owns 128 / RSPLIT columns of one (request, head).  A launch with few columns (a single prompt) takes
-//   few rows a thread and so puts H * V * D / 128 warps on the machine; one with many (a decode step) takes 16
-//   and reads and writes every state once in large pieces.
+//   by RSPLIT neighbouring lanes (4, 8 or 16 rows each, in registers, loaded and stored as 16-byte pieces); a
+//   thread holds those rows of one column or of four neighbouring ones; a block owns 128 / RSPLIT (times four)
+//   columns of one (request, head).  The launch picks the shape (see scan_shape).
 //   Columns never exchange anything, and a sum over a column's rows is taken in one fixed order (four rows at a
-//   time, then a tree over those pieces) whatever the rows a thread, so any cut of a request into steps and any
-//   batch it runs in give the same bits.  The tokens' vectors (32-bit: q, k, and the decays or beta and gate) come
-//   through two stages of shared memory by cp.async, a few tokens a stage, the next stage in flight while this
-//   one is computed; where each thread's copies come from and go to is worked out once, not once a stage.  gla_prepare writes those vectors for the decay-per-channel form (q times its scale, k,
-//   a = sigmoid(z)^(1/tau)) once a token, so the blocks that share a head do not each take the exponentials.
+//   time, then a tree over those pieces) whatever the shape, so any cut of a request into steps and any batch it
+//   runs in give the same bits.  The tokens' vectors (32-bit: q, k, and the decays or beta and gate) come through
+//   two stages of shared memory by cp.async, the next stage in flight while this one is computed; where each
+//   thread's copies come from and go to is worked out once, not once a stage.  The read-outs' sums over a
+//   column's threads are taken for eight tokens at once, off the chain that carries S from token to token.
+//   gla_prepare writes the vectors of the decay-per-channel form (q times its scale, k, a = sigmoid(z)^(1/tau))
+//   once a token, so the blocks that share a head do not each take the exponentials.
 //
 //   conv_prepare (delta rule): a short causal convolution over time per channel on the q, k and v
 //   projections (taps [channels, C], the last tap on the current token; the C - 1 inputs in front of a
@@ -58,54 +59,58 @@ struct ScanParams {
   int heads, kv_share, D, V;
 };
 
-// MODE 0: decay per key channel; MODE 1: delta rule.  RSPLIT threads a column of S, DREG rows each;
-// BATCH tokens a stage of shared memory.
-template <typename TV, int MODE, int DREG, int RSPLIT, int BATCH>
+// MODE 0: decay per key channel; MODE 1: delta rule.  RSPLIT threads a column of S, DREG rows each; a thread
+// holds those rows of CPT neighbouring columns (one load of q, k and the decays then serves CPT columns, and the
+// columns' chains of dependent instructions run interleaved); BATCH tokens a stage of shared memory.
+template <typename TV, int MODE, int DREG, int RSPLIT, int CPT, int BATCH>
 __global__ void __launch_bounds__(SCAN_THREADS)
 state_scan_kernel(ScanParams p) {
   KVB_KERNEL_PROLOGUE(MODE == 0 ? KVB_TAG_GLA_SCAN : KVB_TAG_DELTA_SCAN);
   extern __shared__ __align__(16) float smem[];
   constexpr int DP = DREG * RSPLIT;                 // rows covered (>= D; rows beyond D stay zero)
-  constexpr int COLS = SCAN_THREADS / RSPLIT;       // columns this block owns
+  constexpr int COLS = SCAN_THREADS / RSPLIT * CPT; // columns this block owns
   constexpr int NVEC = MODE == 0 ? 3 : 2;           // q, k (, a)
   constexpr int TOKEN = NVEC * DP + 4;              // floats a token holds in a stage; the last four: beta, gate
   constexpr int STAGE = BATCH * TOKEN;
   constexpr int VPT = (BATCH * COLS + SCAN_THREADS - 1) / SCAN_THREADS;
   constexpr int FPT = (BATCH * NVEC * (DP / 4) + SCAN_THREADS - 1) / SCAN_THREADS;   // 16-byte copies a thread, a stage
   constexpr int J = DREG / 4;
+  constexpr int GROUP = BATCH < 8 ? BATCH : 8;      // tokens whose read-outs are summed over the threads together
   float* const vectors = smem;                      // [2][BATCH][TOKEN]
   float* const values = smem + 2 * STAGE;           // [2][BATCH][COLS]
 
   const int req = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int part = tid % RSPLIT, c = tid / RSPLIT;
-  const int col = blockIdx.z * COLS + c;
+  const int part = tid % RSPLIT, c = tid / RSPLIT * CPT;
+  const int col = blockIdx.z * COLS + c;            // the first of this thread's columns
   const int begin = p.query_start[req], end = p.query_start[req + 1];
   const int D = p.D, V = p.V;
-  const bool live = col < V;
   const int kvh = h / p.kv_share;
   const TV* vg = (const TV*)p.v;
 
   // Thread `part` of a column holds the column's rows part * DREG .. part * DREG + DREG - 1 as J 16-byte pieces.
   // In shared memory a vector's piece n lies at place (n % J) * RSPLIT + n / J, so that for one j the parts of a
   // column read neighbouring pieces.
-  float* S_column = p.state + (size_t)p.state_slots[req] * p.state_stride + p.state_offset +
-                    ((size_t)h * V + (live ? col : 0)) * D;
-  float S[DREG];
+  float* const S_head = p.state + (size_t)p.state_slots[req] * p.state_stride + p.state_offset + (size_t)h * V * D;
+  float S[CPT][DREG];
 #pragma unroll
-  for (int j = 0; j < J; ++j) {
-    const int row = part * DREG + 4 * j;
-    float4 s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (live && row < D) {
-      if (p.state16) {
-        s4 = *reinterpret_cast<const float4*>(S_column + row);
-      } else {
-        s4.x = S_column[row];
-        if (row + 1 < D) s4.y = S_column[row + 1];
-        if (row + 2 < D) s4.z = S_column[row + 2];
-        if (row + 3 < D) s4.w = S_column[row + 3];
+  for (int cc = 0; cc < CPT; ++cc) {
+    const float* S_column = S_head + (size_t)(col + cc < V ? col + cc : 0) * D;
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      const int row = part * DREG + 4 * j;
+      float4 s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (col + cc < V && row < D) {
+        if (p.state16) {
+          s4 = *reinterpret_cast<const float4*>(S_column + row);
+        } else {
+          s4.x = S_column[row];
+          if (row + 1 < D) s4.y = S_column[row + 1];
+          if (row + 2 < D) s4.z = S_column[row + 2];
+          if (row + 3 < D) s4.w = S_column[row + 3];
+        }
       }
+      S[cc][4 * j] = s4.x; S[cc][4 * j + 1] = s4.y; S[cc][4 * j + 2] = s4.z; S[cc][4 * j + 3] = s4.w;
     }
-    S[4 * j] = s4.x; S[4 * j + 1] = s4.y; S[4 * j + 2] = s4.z; S[4 * j + 3] = s4.w;
   }
   auto place = [](int row) { return (((row >> 2) % J) * RSPLIT + (row >> 2) / J) * 4 + (row & 3); };
   if (D < DP)                                       // rows beyond D read zeros whatever the stage holds
@@ -152,81 +157,119 @@ state_scan_kernel(ScanParams p) {
                    ((e & 1) ? p.gate : p.beta) + (size_t)(t0 + tt) * p.bg_stride + h);
       }
   };
-  float held[VPT];
-  auto load_values = [&](int t0, int nb) {          // this block's columns of v, into registers
+  // This block's columns of v pass through registers, as they were stored: a conversion at the load would wait
+  // for the load at the top of every stage.
+  TV held[VPT];
+  auto load_values = [&](int t0, int nb) {
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int e = tid + j * SCAN_THREADS, tt = e / COLS, cc = blockIdx.z * COLS + e % COLS;
-      held[j] = (tt < nb && cc < V) ? to_float(vg[(long long)(t0 + tt) * p.v_token + (long long)h * V + cc]) : 0.0f;
+      if (tt < nb && cc < V) held[j] = vg[(long long)(t0 + tt) * p.v_token + (long long)h * V + cc];
     }
   };
-  auto store_values = [&](int stage) {
+  auto store_values = [&](int stage, int nb) {
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
-      const int e = tid + j * SCAN_THREADS;
-      if (e < BATCH * COLS) values[stage * BATCH * COLS + e] = held[j];
+      const int e = tid + j * SCAN_THREADS, tt = e / COLS, cc = blockIdx.z * COLS + e % COLS;
+      if (e < BATCH * COLS) values[stage * BATCH * COLS + e] = (tt < nb && cc < V) ? to_float(held[j]) : 0.0f;
     }
   };
-  // One token: the state's step and the read-out of this thread's column.  A sum over a column's rows is taken
-  // piece by piece (four rows, in order), and the pieces are added as a tree over their numbers (n with n ^ 1,
-  // then with n ^ 2, ...): inside a thread for the pieces it holds, by shuffles between the threads of a column.
-  // The result has the same bits for every DREG, so a launch may pick DREG by how many columns it has.
-  auto tree = [&](float (&piece)[J]) {
+  // One token: the state's step and this thread's part of the read-out of each of its columns.  A sum over a
+  // column's rows is taken piece by piece (four rows, in order), and the pieces are added as a tree over their
+  // numbers (n with n ^ 1, then with n ^ 2, ...): inside a thread for the pieces it holds, by shuffles between the
+  // threads of a column.  The result has the same bits for every DREG and CPT, so a launch may pick both by how
+  // many columns it has.
+  auto own = [&](const float (&piece)[J]) {         // the pieces this thread holds
     float sum = piece[0];
     if constexpr (J == 2) sum = piece[0] + piece[1];
     if constexpr (J == 4) sum = (piece[0] + piece[1]) + (piece[2] + piece[3]);
-#pragma unroll
-    for (int m = 1; m < RSPLIT; m <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
     return sum;
   };
-  auto token = [&](const float* q, float v, float* out_at) {
+  // The sums over the column's threads of the read-out are left to the caller, who takes them for all tokens of
+  // a stage at once: those shuffles do not wait for one another, and the state's step does not wait for them.
+  auto token = [&](const float* q, const float* vs, float (&o_own)[CPT]) {
     const float* k = q + DP;
-    float o[J];
+    float v[CPT];
+    if constexpr (CPT == 4) {
+      const float4 v4 = *reinterpret_cast<const float4*>(vs);
+      v[0] = v4.x; v[1] = v4.y; v[2] = v4.z; v[3] = v4.w;
+    } else {
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) v[cc] = vs[cc];
+    }
+    float4 k4[J], q4[J];
+#pragma unroll
+    for (int j = 0; j < J; ++j) {
+      k4[j] = *reinterpret_cast<const float4*>(k + (j * RSPLIT + part) * 4);
+      q4[j] = *reinterpret_cast<const float4*>(q + (j * RSPLIT + part) * 4);
+    }
+    float o[CPT][J];
     if (MODE == 0) {
       const float* a = k + DP;
 #pragma unroll
       for (int j = 0; j < J; ++j) {
-        const int at = (j * RSPLIT + part) * 4, i = 4 * j;
-        const float4 a4 = *reinterpret_cast<const float4*>(a + at);
-        const float4 k4 = *reinterpret_cast<const float4*>(k + at);
-        const float4 q4 = *reinterpret_cast<const float4*>(q + at);
-        S[i] = fmaf(k4.x, v, a4.x * S[i]);
-        S[i + 1] = fmaf(k4.y, v, a4.y * S[i + 1]);
-        S[i + 2] = fmaf(k4.z, v, a4.z * S[i + 2]);
-        S[i + 3] = fmaf(k4.w, v, a4.w * S[i + 3]);
-        o[j] = fmaf(S[i + 3], q4.w, fmaf(S[i + 2], q4.z, fmaf(S[i + 1], q4.y, S[i] * q4.x)));
+        const float4 a4 = *reinterpret_cast<const float4*>(a + (j * RSPLIT + part) * 4);
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          float* s = &S[cc][4 * j];
+          s[0] = fmaf(k4[j].x, v[cc], a4.x * s[0]);
+          s[1] = fmaf(k4[j].y, v[cc], a4.y * s[1]);
+          s[2] = fmaf(k4[j].z, v[cc], a4.z * s[2]);
+          s[3] = fmaf(k4[j].w, v[cc], a4.w * s[3]);
+          o[cc][j] = fmaf(s[3], q4[j].w, fmaf(s[2], q4[j].z, fmaf(s[1], q4[j].y, s[0] * q4[j].x)));
+        }
       }
     } else {
       const float beta = q[NVEC * DP], g = q[NVEC * DP + 1];
-      float4 k4[J];
-      float d[J];
+      float dot[CPT];
 #pragma unroll
-      for (int j = 0; j < J; ++j) {
-        const int i = 4 * j;
-        k4[j] = *reinterpret_cast<const float4*>(k + (j * RSPLIT + part) * 4);
-        S[i] *= g; S[i + 1] *= g; S[i + 2] *= g; S[i + 3] *= g;
-        d[j] = fmaf(S[i + 3], k4[j].w, fmaf(S[i + 2], k4[j].z, fmaf(S[i + 1], k4[j].y, S[i] * k4[j].x)));
+      for (int cc = 0; cc < CPT; ++cc) {
+        float d[J];
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          float* s = &S[cc][4 * j];
+          s[0] *= g; s[1] *= g; s[2] *= g; s[3] *= g;
+          d[j] = fmaf(s[3], k4[j].w, fmaf(s[2], k4[j].z, fmaf(s[1], k4[j].y, s[0] * k4[j].x)));
+        }
+        dot[cc] = own(d);
       }
-      const float u = beta * (v - tree(d));
 #pragma unroll
-      for (int j = 0; j < J; ++j) {
-        const int i = 4 * j;
-        const float4 q4 = *reinterpret_cast<const float4*>(q + (j * RSPLIT + part) * 4);
-        S[i] = fmaf(k4[j].x, u, S[i]);
-        S[i + 1] = fmaf(k4[j].y, u, S[i + 1]);
-        S[i + 2] = fmaf(k4[j].z, u, S[i + 2]);
-        S[i + 3] = fmaf(k4[j].w, u, S[i + 3]);
-        o[j] = fmaf(S[i + 3], q4.w, fmaf(S[i + 2], q4.z, fmaf(S[i + 1], q4.y, S[i] * q4.x)));
+      for (int m = 1; m < RSPLIT; m <<= 1)
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) dot[cc] += __shfl_xor_sync(0xffffffffu, dot[cc], m);
+#pragma unroll
+      for (int cc = 0; cc < CPT; ++cc) {
+        const float u = beta * (v[cc] - dot[cc]);
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          float* s = &S[cc][4 * j];
+          s[0] = fmaf(k4[j].x, u, s[0]);
+          s[1] = fmaf(k4[j].y, u, s[1]);
+          s[2] = fmaf(k4[j].z, u, s[2]);
+          s[3] = fmaf(k4[j].w, u, s[3]);
+          o[cc][j] = fmaf(s[3], q4[j].w, fmaf(s[2], q4[j].z, fmaf(s[1], q4[j].y, s[0] * q4[j].x)));
+        }
       }
     }
-    const float sum = tree(o);
-    if (live && part == 0) *out_at = sum;
+#pragma unroll
+    for (int cc = 0; cc < CPT; ++cc) o_own[cc] = own(o[cc]);
+  };
+  const bool out16 = CPT == 4 && (V & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
+  auto write_out = [&](float* at, const float (&sum)[CPT]) {      // the thread with part 0 writes its columns
+    if (part != 0) return;
+    if (CPT == 4 && out16 && col < V) {
+      *reinterpret_cast<float4*>(at) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+      return;
+    }
+#pragma unroll
+    for (int cc = 0; cc < CPT; ++cc)
+      if (col + cc < V) at[cc] = sum[cc];
   };
 
   if (begin < end) {
     fetch(0, begin, min(BATCH, end - begin));
     load_values(begin, min(BATCH, end - begin));
-    store_values(0);
+    store_values(0, min(BATCH, end - begin));
   }
   scan_copies_done();
   __syncthreads();
@@ -241,76 +284,124 @@ state_scan_kernel(ScanParams p) {
     }
     const float* st = vectors + stage * STAGE;
     const float* vs = values + stage * BATCH * COLS + c;
-    float* out_at = p.out + ((size_t)t0 * p.heads + h) * V + (live ? col : 0);
+    float* out_at = p.out + ((size_t)t0 * p.heads + h) * V + (col < V ? col : 0);
     if (nb == BATCH) {                                // a full stage: nothing to ask between its tokens
 #pragma unroll
-      for (int tt = 0; tt < BATCH; ++tt) token(st + tt * TOKEN, vs[tt * COLS], out_at + tt * out_token);
+      for (int g = 0; g < BATCH; g += GROUP) {
+        float sums[GROUP][CPT];
+#pragma unroll
+        for (int tt = 0; tt < GROUP; ++tt) token(st + (g + tt) * TOKEN, vs + (g + tt) * COLS, sums[tt]);
+#pragma unroll
+        for (int m = 1; m < RSPLIT; m <<= 1)
+#pragma unroll
+          for (int tt = 0; tt < GROUP; ++tt)
+#pragma unroll
+            for (int cc = 0; cc < CPT; ++cc) sums[tt][cc] += __shfl_xor_sync(0xffffffffu, sums[tt][cc], m);
+#pragma unroll
+        for (int tt = 0; tt < GROUP; ++tt) write_out(out_at + (g + tt) * out_token, sums[tt]);
+      }
     } else {
-      for (int tt = 0; tt < nb; ++tt) token(st + tt * TOKEN, vs[tt * COLS], out_at + tt * out_token);
+      for (int tt = 0; tt < nb; ++tt) {
+        float sum[CPT];
+        token(st + tt * TOKEN, vs + tt * COLS, sum);
+#pragma unroll
+        for (int m = 1; m < RSPLIT; m <<= 1)
+#pragma unroll
+          for (int cc = 0; cc < CPT; ++cc) sum[cc] += __shfl_xor_sync(0xffffffffu, sum[cc], m);
+        write_out(out_at + tt * out_token, sum);
+      }
     }
-    if (next < end) store_values(stage ^ 1);
+    if (next < end) store_values(stage ^ 1, next_nb);
     scan_copies_done();
     __syncthreads();
   }
-  if (live)
+#pragma unroll
+  for (int cc = 0; cc < CPT; ++cc) {
+    if (col + cc >= V) continue;
+    float* S_column = S_head + (size_t)(col + cc) * D;
 #pragma unroll
     for (int j = 0; j < J; ++j) {
       const int row = part * DREG + 4 * j;
       if (row < D) {
         if (p.state16) {
-          *reinterpret_cast<float4*>(S_column + row) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+          *reinterpret_cast<float4*>(S_column + row) =
+              make_float4(S[cc][4 * j], S[cc][4 * j + 1], S[cc][4 * j + 2], S[cc][4 * j + 3]);
         } else {
-          S_column[row] = S[4 * j];
-          if (row + 1 < D) S_column[row + 1] = S[4 * j + 1];
-          if (row + 2 < D) S_column[row + 2] = S[4 * j + 2];
-          if (row + 3 < D) S_column[row + 3] = S[4 * j + 3];
+          S_column[row] = S[cc][4 * j];
+          if (row + 1 < D) S_column[row + 1] = S[cc][4 * j + 1];
+          if (row + 2 < D) S_column[row + 2] = S[cc][4 * j + 2];
+          if (row + 3 < D) S_column[row + 3] = S[cc][4 * j + 3];
         }
       }
     }
+  }
 }
 
-// Rows of S a thread holds.  Sums over a column come out with the same bits whatever the choice, so it follows
-// the launch: 16 rows a thread when that already gives every SM three blocks (many requests, or a decode step,
-// where each block then moves 8 KB of state and more), else 8, else 4 (a single prompt has only H * V columns to
-// offer, and one token's step is a chain of dependent instructions that only more warps can hide).
-static int scan_rows_per_thread(int D, long long columns_of_all_heads, int V) {
-  const long long wanted = 3LL * (kvb_sm_count() > 0 ? kvb_sm_count() : 148);
-  const char* asked = getenv("KVCORE_SCAN_ROWS");     // tests run every choice on one input and compare the bits
-  const int most = asked && (atoi(asked) == 4 || atoi(asked) == 8) ? atoi(asked) : 16;
-  const bool forced = asked && atoi(asked) == most;
-  for (int rows = most; rows > 4; rows >>= 1) {
-    int rsplit = 1;
-    while (rows * rsplit < D) rsplit *= 2;
-    const int cols = SCAN_THREADS / rsplit;
-    if (rows * 32 < D) break;
-    if (forced || columns_of_all_heads / V * ((V + cols - 1) / cols) >= wanted) return rows;
-  }
-  int rows = 4;
-  while (rows * 32 < D) rows *= 2;
-  return rows;
+// Rows of S a thread holds, how many neighbouring columns, and how many tokens a stage.  Sums over a column come
+// out with the same bits whatever the choice, so it follows the launch (timed at keys of 128 entries, 2,048 to
+// 4,096 columns a request).  A step of single tokens moves every state once and does little else: 8 rows of four
+// columns, stages of two tokens (6 KB a block, so that many blocks share an SM).  A step with prompts in it is a
+// chain of dependent instructions per token, and the stages' hand-overs cost as much as their tokens: stages of
+// 16 tokens; the delta rule, whose chain passes through a sum over the column's threads, 16 rows of one column
+// (three shuffles in the chain, not five); the decay per channel, whose chain stays inside a thread, 8 or 4 rows
+// of four columns (one load of q, k and the decays serves four columns) while that still fills the SMs, else 4
+// rows of one column, which gives four times the warps.
+struct ScanShape { int rows, cols; bool brief; };
+static long long scan_blocks(int D, long long heads_of_all, int V, int rows, int cols) {
+  int rsplit = 1;
+  while (rows * rsplit < D) rsplit *= 2;
+  const int owned = SCAN_THREADS / rsplit * cols;
+  return heads_of_all * ((V + owned - 1) / owned);
+}
+static ScanShape scan_shape(int mode, int D, long long heads_of_all, int V, bool brief) {
+  const long long sms = kvb_sm_count() > 0 ? kvb_sm_count() : 148;
+  int least = 4;                                      // 32 threads a column at most
+  while (least * 32 < D) least *= 2;
+  // tests run every choice on one input and compare the bits
+  const char* rows_asked = getenv("KVCORE_SCAN_ROWS");
+  const char* cols_asked = getenv("KVCORE_SCAN_COLS");
+  const int r = rows_asked ? atoi(rows_asked) : 0, c = cols_asked ? atoi(cols_asked) : 0;
+  if ((r == 4 || r == 8 || r == 16) && r >= least) return {r, (c == 4 && r <= 8) ? 4 : 1, false};
+  if (c == 4) return {least, least <= 8 ? 4 : 1, brief && least == 8};
+  if (c == 1) return {least, 1, false};
+  if (brief) return least <= 8 ? ScanShape{8, 4, true} : ScanShape{16, 1, true};
+  if (mode == 1) return {16, 1, false};
+  if (least <= 8 && scan_blocks(D, heads_of_all, V, 8, 4) >= 2 * sms) return {8, 4, false};
+  if (least <= 4 && scan_blocks(D, heads_of_all, V, 4, 4) >= sms) return {4, 4, false};
+  return {least, 1, false};
 }
 
 template <typename TV, int MODE>
-static int launch_state_scan(const ScanParams& p_in, int num_reqs, cudaStream_t stream) {
+static int launch_state_scan(const ScanParams& p_in, int num_reqs, long long tokens, cudaStream_t stream) {
   ScanParams p = p_in;
   KVB_REQUIRE(p.D <= 512, "state_scan: keys wider than 512 entries");
-  const int dreg = scan_rows_per_thread(p.D, (long long)num_reqs * p.heads * p.V, p.V);
+  const ScanShape shape = scan_shape(MODE, p.D, (long long)num_reqs * p.heads, p.V, tokens <= 2LL * num_reqs);
+  const int dreg = shape.rows, cpt = shape.cols;
   int rsplit = 1;
   while (dreg * rsplit < p.D) rsplit *= 2;
   p.vec16 = (p.D % 4 == 0 && p.vec_token % 4 == 0 && ((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.a) % 16 == 0) ? 1 : 0;
   p.state16 = (p.D % 4 == 0 && p.state_stride % 4 == 0 && p.state_offset % 4 == 0 && (uintptr_t)p.state % 16 == 0) ? 1 : 0;
-  const int cols = SCAN_THREADS / rsplit;
+  const int cols = SCAN_THREADS / rsplit * cpt;
   const dim3 grid(num_reqs, p.heads, (p.V + cols - 1) / cols), block(SCAN_THREADS);
   cudaError_t err = cudaErrorInvalidValue;
-#define SCAN_CASE(DR, RS)                                                                                     \
-  if (dreg == DR && rsplit == RS) {                                                                           \
-    constexpr int B = DR * RS <= 128 ? 8 : 1024 / (DR * RS);                                                  \
-    const size_t smem = 2 * (size_t)B * ((MODE == 0 ? 3 : 2) * DR * RS + 4 + SCAN_THREADS / RS) * sizeof(float); \
-    err = kvb_launch((state_scan_kernel<TV, MODE, DR, RS, B>), grid, block, smem, stream, true, p);           \
+#define SCAN_CASE(DR, RS, CP, BRIEF)                                                                          \
+  if (dreg == DR && rsplit == RS && cpt == CP && shape.brief == BRIEF) {                                      \
+    constexpr int B = BRIEF ? 2 : DR * RS <= 128 ? 16 : 2048 / (DR * RS);                                     \
+    const size_t smem = 2 * (size_t)B * ((MODE == 0 ? 3 : 2) * DR * RS + 4 + SCAN_THREADS / RS * CP) * sizeof(float); \
+    static bool allowed = false;                      /* more than 48 KB a block is asked for once */         \
+    if (smem > 48 * 1024 && !allowed) {                                                                       \
+      KVB_CHECK_CUDA(cudaFuncSetAttribute(state_scan_kernel<TV, MODE, DR, RS, CP, B>,                         \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));           \
+      allowed = true;                                                                                         \
+    }                                                                                                         \
+    err = kvb_launch((state_scan_kernel<TV, MODE, DR, RS, CP, B>), grid, block, smem, stream, true, p);       \
   }
-  SCAN_CASE(4, 1) SCAN_CASE(4, 2) SCAN_CASE(4, 4) SCAN_CASE(4, 8) SCAN_CASE(4, 16) SCAN_CASE(4, 32)
-  SCAN_CASE(8, 1) SCAN_CASE(8, 2) SCAN_CASE(8, 4) SCAN_CASE(8, 8) SCAN_CASE(8, 16) SCAN_CASE(8, 32)
-  SCAN_CASE(16, 1) SCAN_CASE(16, 2) SCAN_CASE(16, 4) SCAN_CASE(16, 8) SCAN_CASE(16, 16) SCAN_CASE(16, 32)
+#define SCAN_ROWS(DR, CP, BRIEF)                                                                              \
+  SCAN_CASE(DR, 1, CP, BRIEF) SCAN_CASE(DR, 2, CP, BRIEF) SCAN_CASE(DR, 4, CP, BRIEF) SCAN_CASE(DR, 8, CP, BRIEF) \
+  SCAN_CASE(DR, 16, CP, BRIEF) SCAN_CASE(DR, 32, CP, BRIEF)
+  SCAN_ROWS(4, 1, false) SCAN_ROWS(8, 1, false) SCAN_ROWS(16, 1, false) SCAN_ROWS(4, 4, false) SCAN_ROWS(8, 4, false)
+  SCAN_ROWS(16, 1, true) SCAN_ROWS(8, 4, true)
+#undef SCAN_ROWS
 #undef SCAN_CASE
   KVB_CHECK_CUDA(err);
   KVB_CHECK_LAUNCH();
@@ -363,13 +454,14 @@ extern "C" int kvb_gla_scan(float* out, float* prepared, const void* q, const vo
   p.out = out; p.state = state; p.state_stride = state_stride; p.state_offset = state_offset;
   p.query_start = query_start; p.state_slots = state_slots;
   p.heads = heads; p.kv_share = 1; p.D = D; p.V = V;
-  return dtype == KVB_F32 ? launch_state_scan<float, 0>(p, num_reqs, stream) : launch_state_scan<bf16, 0>(p, num_reqs, stream);
+  return dtype == KVB_F32 ? launch_state_scan<float, 0>(p, num_reqs, tokens, stream)
+                          : launch_state_scan<bf16, 0>(p, num_reqs, tokens, stream);
 }
 
 // Delta rule.  prepared [T, 2 * G * D + H * V + 2 * H] 32-bit as conv_prepare leaves it: q, k (G heads), v, beta, gate.
 extern "C" int kvb_delta_scan(float* out, const float* prepared, float* state, long long state_stride,
-                              long long state_offset, const int* query_start, const int* state_slots, int num_reqs,
-                              int heads, int kv_heads, int D, int V, cudaStream_t stream) {
+                              long long state_offset, const int* query_start, const int* state_slots, int tokens,
+                              int num_reqs, int heads, int kv_heads, int D, int V, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   KVB_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && D > 0 && V > 0, "delta_scan: bad sizes");
   KVB_REQUIRE(heads <= 65535, "delta_scan: too many heads");
@@ -383,7 +475,7 @@ extern "C" int kvb_delta_scan(float* out, const float* prepared, float* state, l
   p.beta = prepared + 2 * (size_t)kv_heads * D + (size_t)heads * V;
   p.gate = p.beta + heads;
   p.bg_stride = width;
-  return launch_state_scan<float, 1>(p, num_reqs, stream);
+  return launch_state_scan<float, 1>(p, num_reqs, tokens, stream);
 }
 
 // ---- short convolution, activations, unit vectors, step sizes --------------------------------------------------

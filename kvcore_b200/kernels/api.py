@@ -89,7 +89,7 @@ def ensure_built(verbose: bool = False) -> str:
                                  _int, _vp, _vp, _vp, _int, _vp],
         "kvb_gla_scan": [_vp, _vp, _vp, _vp, _vp, _ll, _vp, _ll, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _int,
                          _float, _float, _int, _vp],
-        "kvb_delta_scan": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _int, _vp],
+        "kvb_delta_scan": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _int, _int, _vp],
         "kvb_conv_prepare": [_vp, _vp, _ll, _vp, _int, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int,
                              _int, _int, _int, _int, _float, _float, _int, _vp],
         "kvb_gated_rms_norm": [_vp, _ll, _vp, _vp, _ll, _vp, _int, _int, _int, _float, _float, _int, _vp],
@@ -1448,8 +1448,8 @@ def delta_scan(prepared: torch.Tensor, state: torch.Tensor, ctx, *, heads: int, 
     _state_row(state, state_offset, heads * dim * value_dim)
     out = torch.empty((prepared.shape[0], heads, value_dim), dtype=torch.float32, device=prepared.device)
     _call("kvb_delta_scan", out.data_ptr(), prepared.data_ptr(), state.data_ptr(), state.stride(0), state_offset,
-          ctx.query_start.data_ptr(), ctx.state_slots.data_ptr(), ctx.num_reqs, heads, kv_heads, dim, value_dim,
-          _stream())
+          ctx.query_start.data_ptr(), ctx.state_slots.data_ptr(), prepared.shape[0], ctx.num_reqs, heads, kv_heads,
+          dim, value_dim, _stream())
     return out
 
 

@@ -35,10 +35,20 @@ class _HostBatch:
         self.num_reqs = batch.num_reqs
 
 
+@pytest.fixture(params=[None, "4"], ids=["columns-chosen", "columns-4"])
+def columns_a_thread(request, monkeypatch):
+    """The scans with the columns a thread holds left to the launch, and with four wherever the key width allows."""
+    if request.param is None:
+        monkeypatch.delenv("KVCORE_SCAN_COLS", raising=False)
+    else:
+        monkeypatch.setenv("KVCORE_SCAN_COLS", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("front", [3, 8])      # the state begins `front` floats into its row: off and on a 16-byte boundary
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,dim,vdim", SCAN_SIZES)
-def test_decay_per_channel_scan(dtype, heads, dim, vdim, front):
+def test_decay_per_channel_scan(dtype, heads, dim, vdim, front, columns_a_thread):
     batch = _Batch(SCAN_LENS, slots=[4, 0, 2, 5])
     tokens = batch.num_tokens
     rows = randn(tokens, 2 * heads * dim + heads * vdim + 8, dtype=dtype, seed=1)
@@ -56,7 +66,7 @@ def test_decay_per_channel_scan(dtype, heads, dim, vdim, front):
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(4, 2, 6, 10), (2, 2, 16, 24), (6, 3, 32, 72), (2, 1, 64, 200),
                                                      (4, 1, 128, 40), (1, 1, 200, 20), (2, 2, 256, 12), (2, 1, 512, 8)])
 @pytest.mark.parametrize("front", [7, 4])
-def test_delta_rule_scan(heads, kv_heads, dim, vdim, front):
+def test_delta_rule_scan(heads, kv_heads, dim, vdim, front, columns_a_thread):
     batch = _Batch(SCAN_LENS, slots=[1, 3, 0, 2])
     tokens, qk = batch.num_tokens, kv_heads * dim
     prepared = randn(tokens, 2 * qk + heads * vdim + 2 * heads, dtype=torch.float32, seed=4)
@@ -106,20 +116,23 @@ def test_scans_do_not_depend_on_the_cut(kind):
         assert not state[:2].any()
 
 
-@pytest.mark.parametrize("dim,vdim", [(40, 24), (128, 40), (200, 12), (512, 8)])
+@pytest.mark.parametrize("dim,vdim", [(40, 24), (128, 40), (128, 13), (200, 12), (512, 8)])
 @pytest.mark.parametrize("kind", ["decay", "delta"])
 def test_scans_do_not_depend_on_the_rows_a_thread_holds(kind, dim, vdim, monkeypatch):
-    """A launch picks how many rows of a column one thread holds by the columns it has (a single prompt, or a
-    batch of many requests): every choice gives the same bits, out and in the state."""
-    heads, kv_heads, lens = 2, 1, [(0, 13), (0, 1), (0, 6)]
+    """A launch picks how many rows of a column one thread holds, and of how many neighbouring columns, by the
+    columns it has (a single prompt, or a batch of many requests): every choice gives the same bits, out and in
+    the state.  The prompts hold full stages of tokens and a rest."""
+    heads, kv_heads, lens = 2, 1, [(0, 29), (0, 1), (0, 6)]
     batch = _Batch(lens, slots=[2, 0, 1])
     tokens = batch.num_tokens
     seen = []
-    for rows_a_thread in (None, "4", "8", "16"):
-        if rows_a_thread is None:
-            monkeypatch.delenv("KVCORE_SCAN_ROWS", raising=False)
-        else:
-            monkeypatch.setenv("KVCORE_SCAN_ROWS", rows_a_thread)
+    for rows_a_thread, columns_a_thread in ((None, None), ("4", "1"), ("8", "1"), ("16", "1"), ("4", "4"), ("8", "4"),
+                                            (None, "4"), (None, "1")):
+        for name, value in (("KVCORE_SCAN_ROWS", rows_a_thread), ("KVCORE_SCAN_COLS", columns_a_thread)):
+            if value is None:
+                monkeypatch.delenv(name, raising=False)
+            else:
+                monkeypatch.setenv(name, value)
         state, _ = _states(3, heads * dim * vdim, seed=21)
         if kind == "decay":
             rows = randn(tokens, 2 * heads * dim + heads * vdim, seed=22, dtype=torch.float32)
