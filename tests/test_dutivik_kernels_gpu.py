@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_kernels as P
-from test_kernels_gpu import DEV, DTYPES, K, randn, tol
+from test_kernels_gpu import DEV, DTYPES, K, _cache_case, randn, tol
 from test_pipesun_kernels_gpu import _Batch
 
 pytestmark = pytest.mark.gpu
@@ -262,3 +262,56 @@ def test_turn_norm_and_cache_write(dtype, q_heads, k_heads, dim, rot, vwidth, no
     torch.testing.assert_close(rows.cpu()[:, :qc], host_rows[:, :qc], **close)
     torch.testing.assert_close(rows.cpu()[:, qc:], host_rows[:, qc:], rtol=0, atol=0)      # k, v, gates: untouched
     torch.testing.assert_close(cache.cpu(), host_cache, **close)
+
+
+# dtype, key width, value width, page, (cached, new), window: the edge among the step's own tokens and in the cache,
+# inside a page and on its border, in prompts (tiles and the general kernel) and decoded (keys in chunks too)
+WINDOW_EDGES = [
+    (torch.float32, 20, 12, 4, (0, 40), 9),
+    (torch.float32, 20, 12, 4, (39, 1), 8),
+    (torch.float32, 48, 48, 16, (70, 3), 40),
+    (torch.bfloat16, 64, 128, 16, (100, 201), 50),
+    (torch.bfloat16, 64, 128, 16, (300, 5), 48),
+    (torch.bfloat16, 128, 64, 16, (640, 1), 100),
+    (torch.bfloat16, 128, 64, 16, (1000, 1), 513),
+    (torch.bfloat16, 48, 48, 16, (90, 1), 1),
+]
+
+
+@pytest.mark.parametrize("dtype,dim,vdim,page,lens,window", WINDOW_EDGES)
+@pytest.mark.parametrize("place", ["inside", "outside"])
+def test_the_window_s_edge(dtype, dim, vdim, page, lens, window, place):
+    """A row at position p sees positions p - window + 1 .. p.  One key is made to dominate the last row's flat
+    scores by scaling it along the query: at p - window + 1 the output is that key's value; at p - window, with a
+    huge value, it leaves no trace.  The cached row is [k of all kv heads | v of all kv heads]."""
+    heads, kv_heads = 4, 2
+    context, query = lens
+    last = context + query - 1
+    position = last - window + (1 if place == "inside" else 0)
+    if position < 0:
+        pytest.skip("nothing lies in front of the first position")
+    width = kv_heads * (dim + vdim)
+    case = _cache_case(dtype, 1, 1, width, page, [lens], seed=23)
+    plane, batch = case["k_cache"], _Batch([lens])
+    q = randn(batch.num_tokens, heads * dim, dtype=dtype, seed=29).view(batch.num_tokens, heads, dim) * 0.05
+    for h in range(1, heads):
+        q[-1, h] = q[-1, 0]
+    page_id, slot = int(case["table"][0, position // page]), position % page
+    for g in range(kv_heads):
+        plane[page_id, 0, slot, g * dim:(g + 1) * dim] = (q[-1, 0].float() * (12.0 / q[-1, 0].float().pow(2).sum())).to(dtype)
+    value = plane[page_id, 0, slot, kv_heads * dim:].view(kv_heads, vdim)
+    if place == "outside":
+        value.fill_(3.0e4)
+    out = K().attention_dims(q, plane, plane.view(-1)[kv_heads * dim:], case["table"], batch, scale=1.0, window=window,
+                             out_dtype=torch.float32, value_heads=kv_heads, group=heads // kv_heads, maps=1,
+                             key_width=dim, value_width=vdim, key_strides=(page * width, dim, width),
+                             value_strides=(page * width, vdim, width), page_size=page, num_pages=plane.shape[0])
+    assert K().read_status() == 0
+    if place == "outside":
+        assert out[-1].abs().max() < 50.0, "a key one position behind the window reached the row's output"
+    elif window > 1:
+        want = value.float().repeat_interleave(heads // kv_heads, dim=0)
+        torch.testing.assert_close(out[-1], want, rtol=2e-2, atol=3e-2)
+    else:       # a window of one position: the row sees itself alone
+        torch.testing.assert_close(out[-1], value.float().repeat_interleave(heads // kv_heads, dim=0), rtol=1e-2, atol=1e-2)
+
