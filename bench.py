@@ -666,7 +666,7 @@ def dutivik_config(size: dict, kinds: str) -> dict:
         layers.append({"type": "parallel", "mlp": {"kind": "dense", "ff": size["ff"]},
                        "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}})
     return {"architecture": "Dutivik", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-5},
-            "embedding": {"scale": float(size["width"]) ** 0.5}, "layers": layers}
+            "embedding": {"scale": 24.0}, "layers": layers}
 
 
 def llama_config(size: dict) -> dict:

@@ -269,12 +269,12 @@ def test_turn_norm_and_cache_write(dtype, q_heads, k_heads, dim, rot, vwidth, no
 WINDOW_EDGES = [
     (torch.float32, 20, 12, 4, (0, 40), 9),
     (torch.float32, 20, 12, 4, (39, 1), 8),
-    (torch.float32, 48, 48, 16, (70, 3), 40),
+    (torch.float32, 56, 40, 16, (70, 3), 37),
     (torch.bfloat16, 64, 128, 16, (100, 201), 50),
     (torch.bfloat16, 64, 128, 16, (300, 5), 48),
     (torch.bfloat16, 128, 64, 16, (640, 1), 100),
     (torch.bfloat16, 128, 64, 16, (1000, 1), 513),
-    (torch.bfloat16, 48, 48, 16, (90, 1), 1),
+    (torch.bfloat16, 80, 48, 16, (90, 1), 1),
 ]
 
 
