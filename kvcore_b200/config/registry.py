@@ -121,6 +121,9 @@ def _register_stock_architectures() -> None:
 
     register_architecture(DUTIVIK, lambda raw, shapes=None: DutivikConfig.from_dict(raw, shapes).to_model_spec(),
                           reads_tensor_shapes=True)
+    from .rubuvik import ARCHITECTURE as RUBUVIK, RubuvikConfig
+
+    register_architecture(RUBUVIK, lambda raw: RubuvikConfig.from_dict(raw).to_model_spec())
 
 
 _register_stock_architectures()

@@ -11,6 +11,8 @@
 //     grouped-query attention);
 //   * an optional sink per query head: a logit that joins the softmax's denominator once, unscaled,
 //     with no key and no value;
+//   * an optional slope per query head: slope * (query position - key position) is taken off the scaled
+//     score (a linear bias by distance);
 //   * the output is 32-bit or of the cache's type, with token and head strides of its own.
 //
 // One warp owns one (token, query head) row and walks the keys from the first visible position to the
@@ -30,6 +32,7 @@ struct DimsParams {
   const int* table; int table_stride;
   const int* positions; const int* req_index;
   const float* sink;
+  const float* slopes;
   int num_rows, HQ, per_value_head, maps, DK, DV, page_size, num_pages, window;
   float scale;
   int* status;
@@ -62,6 +65,7 @@ attention_dims_rows_kernel(const DimsParams p) {
   float running_max = -INFINITY, running_sum = 0.0f;
   if (p.sink != nullptr) { running_max = p.sink[head]; running_sum = 1.0f; }
   const int first = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  const float slope = p.slopes != nullptr ? p.slopes[head] : 0.0f;
   const T* kbase = (const T*)p.k + (size_t)kh * p.k_head_stride;
   const T* vbase = (const T*)p.v + (size_t)vh * p.v_head_stride;
 
@@ -79,7 +83,7 @@ attention_dims_rows_kernel(const DimsParams p) {
         const T* krow = kbase + (size_t)page * p.k_page_stride + (size_t)(key % p.page_size) * p.k_row_stride;
         float dot = 0.0f;
         for (int d = 0; d < DK; ++d) dot = fmaf(to_float(krow[d]), qv[d], dot);
-        score = dot * p.scale;
+        score = dot * p.scale - slope * (float)(pos - key);
       }
     }
     const float new_max = fmaxf(running_max, warp_max(score));
@@ -120,7 +124,8 @@ extern "C" int kvb_attention_dims_rows(void* out, long long out_token_stride, lo
                                        long long k_row_stride, const void* v, long long v_page_stride,
                                        long long v_head_stride, long long v_row_stride, const int* table,
                                        int table_stride, const int* positions, const int* req_index,
-                                       const float* sink, int tokens, int HQ, int per_value_head, int maps, int DK,
+                                       const float* sink, const float* slopes, int tokens, int HQ, int per_value_head,
+                                       int maps, int DK,
                                        int DV, int page_size, int num_pages, float scale, int window, int dtype,
                                        cudaStream_t stream) {
   if (tokens == 0) return 0;
@@ -139,7 +144,7 @@ extern "C" int kvb_attention_dims_rows(void* out, long long out_token_stride, lo
   p.k = k; p.k_page_stride = k_page_stride; p.k_head_stride = k_head_stride; p.k_row_stride = k_row_stride;
   p.v = v; p.v_page_stride = v_page_stride; p.v_head_stride = v_head_stride; p.v_row_stride = v_row_stride;
   p.table = table; p.table_stride = table_stride; p.positions = positions; p.req_index = req_index;
-  p.sink = sink; p.num_rows = (int)rows; p.HQ = HQ; p.per_value_head = per_value_head; p.maps = maps;
+  p.sink = sink; p.slopes = slopes; p.num_rows = (int)rows; p.HQ = HQ; p.per_value_head = per_value_head; p.maps = maps;
   p.DK = DK; p.DV = DV; p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.scale = scale;
   p.status = status;
   const int blocks = (int)((rows + AD_WARPS - 1) / AD_WARPS);

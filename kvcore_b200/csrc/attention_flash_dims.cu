@@ -1,7 +1,8 @@
 // Paged flash attention for bf16 on tensor cores (mma.sync m16n8k16, fp32 accumulate) when the width of
 // a query/key (DK) and the width of a value (DV) differ: the tensor-core form of attention_dims.cu, with the
 // same parameters (strides of keys and values given apart, several score maps a value head, values that
-// may be the first entries of the key rows, a sink per query head, 32-bit or bf16 output).
+// may be the first entries of the key rows, a sink per query head, a slope per query head times the distance
+// between query and key taken off the score, 32-bit or bf16 output).
 //
 // A block of 4 warps works on one (request, key head, slice of the value width) and one tile of query
 // rows; a row is a (token, query head of the key head's group) pair, so the heads that share a key head
@@ -34,6 +35,7 @@ struct FlashDimsParams {
   const int* table; int table_stride;
   const int* query_start; const int* context_lens;
   const float* sink;
+  const float* slopes;
   int num_reqs, KH, G, maps, DK, DV, page_size, num_pages, window, v_in_k, vsplit, tiles;
   float scale_log2;
   int num_splits;
@@ -203,6 +205,12 @@ flash_dims_kernel(const FlashDimsParams p) {
     row_head[h] = (vh * p.G + (row_valid[h] ? flat % p.G : 0)) * p.maps + map;
   }
 
+  // the row's slope, in units of the base-2 exponent like the scores
+  float row_slope[2] = {0.0f, 0.0f};
+  if (p.slopes != nullptr) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) row_slope[h] = p.slopes[row_head[h]] * 1.4426950408889634f;
+  }
   float o[DBLOCKS][4];
 #pragma unroll
   for (int j = 0; j < DBLOCKS; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
@@ -256,7 +264,7 @@ flash_dims_kernel(const FlashDimsParams p) {
         const int key = t * KEYS + wkey + j * 8 + (lane & 3) * 2 + (e & 1);
         const bool seen = row_valid[h] && key >= key_lo && key < key_hi && key <= row_pos[h] &&
                           (p.window <= 0 || key > row_pos[h] - p.window);
-        const float v = seen ? s[j][e] * p.scale_log2 : -INFINITY;
+        const float v = seen ? fmaf(s[j][e], p.scale_log2, -row_slope[h] * (float)(row_pos[h] - key)) : -INFINITY;
         s[j][e] = v;
         tile_max[h] = fmaxf(tile_max[h], v);
       }
@@ -510,7 +518,8 @@ extern "C" int kvb_flash_dims_attention(void* out, long long out_token_stride, l
                                         long long k_row_stride, const void* v, long long v_page_stride,
                                         long long v_head_stride, long long v_row_stride, const int* table,
                                         int table_stride, const int* query_start, const int* context_lens,
-                                        const float* sink, int num_reqs, int max_query_len, int value_heads,
+                                        const float* sink, const float* slopes, int num_reqs, int max_query_len,
+                                        int value_heads,
                                         int group, int maps, int DK, int DV, int page_size, int num_pages,
                                         float scale, int window, int num_splits, float* scratch,
                                         cudaStream_t stream) {
@@ -534,7 +543,7 @@ extern "C" int kvb_flash_dims_attention(void* out, long long out_token_stride, l
   p.k = (const bf16*)k; p.k_page_stride = k_page_stride; p.k_head_stride = k_head_stride; p.k_row_stride = k_row_stride;
   p.v = (const bf16*)v; p.v_page_stride = v_page_stride; p.v_head_stride = v_head_stride; p.v_row_stride = v_row_stride;
   p.table = table; p.table_stride = table_stride; p.query_start = query_start; p.context_lens = context_lens;
-  p.sink = sink; p.num_reqs = num_reqs; p.KH = value_heads * maps; p.G = group; p.maps = maps; p.DK = DK; p.DV = DV;
+  p.sink = sink; p.slopes = slopes; p.num_reqs = num_reqs; p.KH = value_heads * maps; p.G = group; p.maps = maps; p.DK = DK; p.DV = DV;
   p.page_size = page_size; p.num_pages = num_pages; p.window = window;
   // the values are columns of the key tile when they are the leading entries of the very rows that serve as keys
   p.v_in_k = (k == v && maps == 1 && k_page_stride == v_page_stride && k_head_stride == v_head_stride &&

@@ -170,6 +170,9 @@ struct KvbTrace {
 #define KVB_TAG_HEAD_GATE 42
 #define KVB_TAG_EMBED_SCALED 43
 #define KVB_TAG_GLA_PREPARE 44
+#define KVB_TAG_GELU_MUL 45
+#define KVB_TAG_LIGHTNING_PREPARE 46
+#define KVB_TAG_LIGHTNING_SCAN 47
 
 // 1 when launches should carry the programmatic-serialization attribute (set by the host side).
 extern "C" int kvb_pdl_enabled();

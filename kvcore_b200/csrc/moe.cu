@@ -3,7 +3,10 @@
 //
 //   route:   z = W_router x in 32-bit (one warp per expert row, lane-strided k in a fixed order, butterfly sum);
 //            scores = sigmoid(z) or softmax(z); the `top` largest (lowest index among equals); weights are
-//            the chosen scores, optionally divided by their sum.  Extra rows (a shared expert's gate) are
+//            the chosen scores, optionally divided by their sum.  Optionally the choice goes by
+//            score + correction[e] (the weights stay the scores), only experts of the `keep` best of `groups`
+//            equal groups of neighbouring experts can be chosen (a group's score: its largest choice score),
+//            and the weights are multiplied by a constant.  Extra rows (a shared expert's gate) are
 //            dotted the same way and leave sigmoid(row . x).
 //   align:   pairs p = token * top + slot are laid out expert by expert, each expert's run padded to whole
 //            tiles of MOE_BM rows with -1, with the expert of every tile and the number of tiles used
@@ -36,11 +39,12 @@ __global__ void __launch_bounds__(MOE_ROUTE_THREADS)
 moe_route_kernel(int* __restrict__ ids_out, float* __restrict__ weights_out, float* __restrict__ gate_out,
                  const T* __restrict__ x, long long x_stride, const float* __restrict__ router,
                  const float* __restrict__ gate_rows, int tokens, int E, int R, int K, int top, int score_mode,
-                 int renormalize) {
+                 int renormalize, const float* __restrict__ correction, int groups, int keep, float weight_scale) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_MOE_ROUTE);
   extern __shared__ __align__(16) unsigned char route_smem[];
   T* xs = reinterpret_cast<T*>(route_smem);                                   // [TPB][K]
   float* scores = reinterpret_cast<float*>(route_smem + (size_t)TPB * K * sizeof(T));   // [TPB][E + R]
+  float* choices = scores + (size_t)TPB * (E + R);                                      // [TPB][E + 2 * groups]
   const int token0 = blockIdx.x * TPB;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = MOE_ROUTE_THREADS / 32;
   for (int i = threadIdx.x; i < TPB * K; i += MOE_ROUTE_THREADS) {
@@ -98,62 +102,102 @@ moe_route_kernel(int* __restrict__ ids_out, float* __restrict__ weights_out, flo
     for (int e = lane; e < E; e += 32) sc[e] = sc[e] / sum;
   }
   __syncwarp();
-  float chosen_sum = 0.0f;
-  for (int slot = 0; slot < top; ++slot) {
-    float best = -INFINITY;
-    int best_e = 0x7fffffff;
-    for (int e = lane; e < E; e += 32) {
-      const float v = sc[e];
-      if (v > best) { best = v; best_e = e; }   // ascending e: the lowest index among equals stays
+  // what the choice goes by: the scores, with the correction when there is one
+  float* ch = choices + warp * (E + 2 * groups);
+  for (int e = lane; e < E; e += 32) ch[e] = correction != nullptr ? sc[e] + correction[e] : sc[e];
+  __syncwarp();
+  auto arg_max = [&](const float* values, int count, float& best, int& best_i) {
+    best = -INFINITY;
+    best_i = 0x7fffffff;
+    for (int i = lane; i < count; i += 32) {
+      const float v = values[i];
+      if (v > best) { best = v; best_i = i; }   // ascending i: the lowest index among equals stays
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-      if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
     }
-    if (lane == 0) {
-      ids_out[(size_t)token * top + slot] = best_e;
-      weights_out[(size_t)token * top + slot] = best;
-      sc[best_e] = -INFINITY;
+    if (best_i == 0x7fffffff) best_i = 0;       // nothing but minus infinity or NaN: stay inside the arrays
+  };
+  if (keep < groups) {
+    // a group's score is its largest choice score; experts outside the `keep` best groups cannot be chosen
+    const int per = E / groups;
+    float* gs = ch + E;
+    float* kept = gs + groups;
+    for (int g = lane; g < groups; g += 32) {
+      float m = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, ch[e]);
+      gs[g] = m;
+      kept[g] = 0.0f;
     }
-    chosen_sum += best;
+    __syncwarp();
+    for (int n = 0; n < keep; ++n) {
+      float best; int best_g;
+      arg_max(gs, groups, best, best_g);
+      if (lane == 0) { gs[best_g] = -INFINITY; kept[best_g] = 1.0f; }
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (kept[e / per] == 0.0f) ch[e] = -INFINITY;
     __syncwarp();
   }
-  if (renormalize && lane == 0)
-    for (int slot = 0; slot < top; ++slot) weights_out[(size_t)token * top + slot] /= chosen_sum;
+  float chosen_sum = 0.0f;
+  for (int slot = 0; slot < top; ++slot) {
+    float best; int best_e;
+    arg_max(ch, E, best, best_e);
+    const float weight = sc[best_e];
+    if (lane == 0) {
+      ids_out[(size_t)token * top + slot] = best_e;
+      weights_out[(size_t)token * top + slot] = weight;
+      ch[best_e] = -INFINITY;
+    }
+    chosen_sum += weight;
+    __syncwarp();
+  }
+  if (lane == 0 && (renormalize || weight_scale != 1.0f))
+    for (int slot = 0; slot < top; ++slot) {
+      float w = weights_out[(size_t)token * top + slot];
+      if (renormalize) w /= chosen_sum;
+      weights_out[(size_t)token * top + slot] = w * weight_scale;
+    }
 }
 
 template <typename T, int TPB>
 static int launch_moe_route(int* ids_out, float* weights_out, float* gate_out, const void* x, long long x_stride,
                             const float* router, const float* gate_rows, int tokens, int E, int R, int K, int top,
-                            int score_mode, int renormalize, cudaStream_t stream) {
-  const size_t smem = (size_t)TPB * K * sizeof(T) + (size_t)TPB * (E + R) * sizeof(float);
+                            int score_mode, int renormalize, const float* correction, int groups, int keep,
+                            float weight_scale, cudaStream_t stream) {
+  const size_t smem = (size_t)TPB * K * sizeof(T) + (size_t)TPB * (2 * E + R + 2 * groups) * sizeof(float);
   KVB_REQUIRE(smem <= 200 * 1024, "moe_route: the tokens' rows and scores do not fit in shared memory");
   if (smem > 48 * 1024)
     KVB_CHECK_CUDA(cudaFuncSetAttribute(moe_route_kernel<T, TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   KVB_CHECK_CUDA(kvb_launch((moe_route_kernel<T, TPB>), dim3((tokens + TPB - 1) / TPB), dim3(MOE_ROUTE_THREADS), smem,
                             stream, true, ids_out, weights_out, gate_out, (const T*)x, x_stride, router, gate_rows,
-                            tokens, E, R, K, top, score_mode, renormalize));
+                            tokens, E, R, K, top, score_mode, renormalize, correction, groups, keep, weight_scale));
   return 0;
 }
 
 extern "C" int kvb_moe_route(int* ids_out, float* weights_out, float* gate_out, const void* x, long long x_stride,
                              const float* router, const float* gate_rows, int tokens, int E, int R, int K, int top,
-                             int score_mode, int renormalize, int dtype, cudaStream_t stream) {
+                             int score_mode, int renormalize, const float* correction, int groups, int keep,
+                             float weight_scale, int dtype, cudaStream_t stream) {
   if (tokens == 0) return 0;
   KVB_REQUIRE(E > 0 && K > 0 && top > 0 && top <= E, "moe_route: need 0 < top <= experts");
+  KVB_REQUIRE(groups > 0 && E % groups == 0 && keep > 0 && keep <= groups && (long long)keep * (E / groups) >= top,
+              "moe_route: the kept groups of experts must hold the experts to choose");
   KVB_REQUIRE(R >= 0 && (R == 0 || (gate_rows != nullptr && gate_out != nullptr)), "moe_route: gate rows need their weights and output");
   KVB_REQUIRE(score_mode == 0 || score_mode == 1, "moe_route: unknown score function");
   // a prompt's tokens go eight a block; a few tokens one a block, for the parallelism
   const bool many = tokens >= 256 && (size_t)8 * K * (dtype == KVB_F32 ? 4 : 2) <= 96 * 1024;
   int rc;
   if (dtype == KVB_F32)
-    rc = many ? launch_moe_route<float, 8>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, stream)
-              : launch_moe_route<float, 1>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, stream);
+    rc = many ? launch_moe_route<float, 8>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, correction, groups, keep, weight_scale, stream)
+              : launch_moe_route<float, 1>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, correction, groups, keep, weight_scale, stream);
   else
-    rc = many ? launch_moe_route<bf16, 8>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, stream)
-              : launch_moe_route<bf16, 1>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, stream);
+    rc = many ? launch_moe_route<bf16, 8>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, correction, groups, keep, weight_scale, stream)
+              : launch_moe_route<bf16, 1>(ids_out, weights_out, gate_out, x, x_stride, router, gate_rows, tokens, E, R, K, top, score_mode, renormalize, correction, groups, keep, weight_scale, stream);
   if (rc) return rc;
   KVB_CHECK_LAUNCH();
   return 0;

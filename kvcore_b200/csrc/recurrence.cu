@@ -10,6 +10,10 @@
 //     delta rule with one decay per head:
 //         S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t
 //         with q_t, k_t, v_t, beta_t, g_t as `conv_prepare` left them (32-bit).
+//     one fixed decay a head (lightning attention):
+//         S <- a_h S + k_t v_t^T,                       o_t = S^T q_t
+//         with q_t = silu(.) * q_scale and k_t = silu(.) as `lightning_prepare` left them (32-bit), v_t passed
+//         through SiLU on its way into shared memory, a_h a constant of the model;
 //   S is kept column by column ([H, V, D] in the state row: a column's D rows lie together).  A column is shared
 //   by RSPLIT neighbouring lanes (4, 8 or 16 rows each, in registers, loaded and stored as 16-byte pieces); a
 //   thread holds those rows of one column or of four neighbouring ones; a block owns 128 / RSPLIT (times four)
@@ -29,7 +33,8 @@
 //   `q_scale`), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).  conv_state_update then
 //   moves the last C - 1 inputs of every request into its state row.
 //
-//   gated_rms_norm: out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight * silu(gate[t, h, :]) * scale.
+//   gated_rms_norm: out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight * silu(gate[t, h, :]) * scale
+//   (or sigmoid(gate) in place of silu(gate)).
 #include "common.cuh"
 
 #define SCAN_THREADS 128
@@ -50,6 +55,7 @@ struct ScanParams {
   int vec16;                                // every vector starts on a 16-byte boundary and D is a multiple of 4
   int state16;                              // so does every column of S in the state rows
   const void* v; long long v_token;         // values [V] of head h at v + t * v_token + h * V (elements)
+  int v_silu;                               // the values pass SiLU (in 32-bit) on their way in
   const float* beta; const float* gate;     // [T, H] with row stride bg_stride (delta rule)
   long long bg_stride;
   float* out;                               // [T, H, V]
@@ -59,13 +65,13 @@ struct ScanParams {
   int heads, kv_share, D, V;
 };
 
-// MODE 0: decay per key channel; MODE 1: delta rule.  RSPLIT threads a column of S, DREG rows each; a thread
+// MODE 0: decay per key channel; MODE 1: delta rule; MODE 2: one fixed decay a head (p.a[h]).  RSPLIT threads a column of S, DREG rows each; a thread
 // holds those rows of CPT neighbouring columns (one load of q, k and the decays then serves CPT columns, and the
 // columns' chains of dependent instructions run interleaved); BATCH tokens a stage of shared memory.
 template <typename TV, int MODE, int DREG, int RSPLIT, int CPT, int BATCH>
 __global__ void __launch_bounds__(SCAN_THREADS)
 state_scan_kernel(ScanParams p) {
-  KVB_KERNEL_PROLOGUE(MODE == 0 ? KVB_TAG_GLA_SCAN : KVB_TAG_DELTA_SCAN);
+  KVB_KERNEL_PROLOGUE(MODE == 0 ? KVB_TAG_GLA_SCAN : MODE == 1 ? KVB_TAG_DELTA_SCAN : KVB_TAG_LIGHTNING_SCAN);
   extern __shared__ __align__(16) float smem[];
   constexpr int DP = DREG * RSPLIT;                 // rows covered (>= D; rows beyond D stay zero)
   constexpr int COLS = SCAN_THREADS / RSPLIT * CPT; // columns this block owns
@@ -171,9 +177,14 @@ state_scan_kernel(ScanParams p) {
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int e = tid + j * SCAN_THREADS, tt = e / COLS, cc = blockIdx.z * COLS + e % COLS;
-      if (e < BATCH * COLS) values[stage * BATCH * COLS + e] = (tt < nb && cc < V) ? to_float(held[j]) : 0.0f;
+      if (e < BATCH * COLS) {
+        float x = (tt < nb && cc < V) ? to_float(held[j]) : 0.0f;
+        if (MODE == 2 && p.v_silu) x = x / (1.0f + expf(-x));
+        values[stage * BATCH * COLS + e] = x;
+      }
     }
   };
+  const float head_decay = MODE == 2 ? p.a[h] : 0.0f;
   // One token: the state's step and this thread's part of the read-out of each of its columns.  A sum over a
   // column's rows is taken piece by piece (four rows, in order), and the pieces are added as a tree over their
   // numbers (n with n ^ 1, then with n ^ 2, ...): inside a thread for the pieces it holds, by shuffles between the
@@ -216,6 +227,19 @@ state_scan_kernel(ScanParams p) {
           s[1] = fmaf(k4[j].y, v[cc], a4.y * s[1]);
           s[2] = fmaf(k4[j].z, v[cc], a4.z * s[2]);
           s[3] = fmaf(k4[j].w, v[cc], a4.w * s[3]);
+          o[cc][j] = fmaf(s[3], q4[j].w, fmaf(s[2], q4[j].z, fmaf(s[1], q4[j].y, s[0] * q4[j].x)));
+        }
+      }
+    } else if (MODE == 2) {
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+#pragma unroll
+        for (int cc = 0; cc < CPT; ++cc) {
+          float* s = &S[cc][4 * j];
+          s[0] = fmaf(k4[j].x, v[cc], head_decay * s[0]);
+          s[1] = fmaf(k4[j].y, v[cc], head_decay * s[1]);
+          s[2] = fmaf(k4[j].z, v[cc], head_decay * s[2]);
+          s[3] = fmaf(k4[j].w, v[cc], head_decay * s[3]);
           o[cc][j] = fmaf(s[3], q4[j].w, fmaf(s[2], q4[j].z, fmaf(s[1], q4[j].y, s[0] * q4[j].x)));
         }
       }
@@ -379,7 +403,8 @@ static int launch_state_scan(const ScanParams& p_in, int num_reqs, long long tok
   const int dreg = shape.rows, cpt = shape.cols;
   int rsplit = 1;
   while (dreg * rsplit < p.D) rsplit *= 2;
-  p.vec16 = (p.D % 4 == 0 && p.vec_token % 4 == 0 && ((uintptr_t)p.q | (uintptr_t)p.k | (uintptr_t)p.a) % 16 == 0) ? 1 : 0;
+  p.vec16 = (p.D % 4 == 0 && p.vec_token % 4 == 0 &&
+             ((uintptr_t)p.q | (uintptr_t)p.k | (MODE == 2 ? 0 : (uintptr_t)p.a)) % 16 == 0) ? 1 : 0;
   p.state16 = (p.D % 4 == 0 && p.state_stride % 4 == 0 && p.state_offset % 4 == 0 && (uintptr_t)p.state % 16 == 0) ? 1 : 0;
   const int cols = SCAN_THREADS / rsplit * cpt;
   const dim3 grid(num_reqs, p.heads, (p.V + cols - 1) / cols), block(SCAN_THREADS);
@@ -456,6 +481,53 @@ extern "C" int kvb_gla_scan(float* out, float* prepared, const void* q, const vo
   p.heads = heads; p.kv_share = 1; p.D = D; p.V = V;
   return dtype == KVB_F32 ? launch_state_scan<float, 0>(p, num_reqs, tokens, stream)
                           : launch_state_scan<bf16, 0>(p, num_reqs, tokens, stream);
+}
+
+// What the fixed-decay scan reads, 32-bit [T, 2 * H * D]: silu(q) times q_scale, silu(k).
+template <typename T>
+__global__ void __launch_bounds__(256)
+lightning_prepare_kernel(float* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k,
+                         long long row_stride, long long tokens, int width, float q_scale) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_LIGHTNING_PREPARE);
+  const long long total = tokens * width;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const long long t = e / width;
+    const int i = (int)(e - t * width);
+    float* row = out + t * 2 * width;
+    const float qv = to_float(q[t * row_stride + i]), kv = to_float(k[t * row_stride + i]);
+    row[i] = qv / (1.0f + expf(-qv)) * q_scale;
+    row[width + i] = kv / (1.0f + expf(-kv));
+  }
+}
+
+// One fixed decay a head.  q, k, v: columns of the projected rows (row stride `row_stride`, heads side by side),
+// all three passed through SiLU; decay [H] 32-bit; prepared: scratch, 32-bit [T, 2 * H * D].
+extern "C" int kvb_lightning_scan(float* out, float* prepared, const void* q, const void* k, const void* v,
+                                  long long row_stride, const float* decay, float* state, long long state_stride,
+                                  long long state_offset, const int* query_start, const int* state_slots, int tokens,
+                                  int num_reqs, int heads, int D, int V, float q_scale, int dtype,
+                                  cudaStream_t stream) {
+  if (num_reqs == 0 || tokens == 0) return 0;
+  KVB_REQUIRE(heads > 0 && D > 0 && V > 0 && decay != nullptr, "lightning_scan: bad sizes");
+  KVB_REQUIRE(heads <= 65535, "lightning_scan: too many heads");
+  const int width = heads * D;
+  const long long wanted = ((long long)tokens * width + 255) / 256;
+  const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
+  const dim3 grid((unsigned)(wanted < resident ? wanted : resident));
+  if (dtype == KVB_F32)
+    KVB_CHECK_CUDA(kvb_launch((lightning_prepare_kernel<float>), grid, dim3(256), 0, stream, true, prepared,
+        (const float*)q, (const float*)k, row_stride, (long long)tokens, width, q_scale));
+  else
+    KVB_CHECK_CUDA(kvb_launch((lightning_prepare_kernel<bf16>), grid, dim3(256), 0, stream, true, prepared,
+        (const bf16*)q, (const bf16*)k, row_stride, (long long)tokens, width, q_scale));
+  ScanParams p = {};
+  p.q = prepared; p.k = prepared + width; p.a = decay; p.vec_token = 2LL * width;
+  p.v = v; p.v_token = row_stride; p.v_silu = 1;
+  p.out = out; p.state = state; p.state_stride = state_stride; p.state_offset = state_offset;
+  p.query_start = query_start; p.state_slots = state_slots;
+  p.heads = heads; p.kv_share = 1; p.D = D; p.V = V;
+  return dtype == KVB_F32 ? launch_state_scan<float, 2>(p, num_reqs, tokens, stream)
+                          : launch_state_scan<bf16, 2>(p, num_reqs, tokens, stream);
 }
 
 // Delta rule.  prepared [T, 2 * G * D + H * V + 2 * H] 32-bit as conv_prepare leaves it: q, k (G heads), v, beta, gate.
@@ -602,7 +674,7 @@ template <typename T>
 __global__ void __launch_bounds__(CP_THREADS)
 gated_rms_norm_kernel(T* __restrict__ out, long long out_stride, const float* __restrict__ o,
                       const T* __restrict__ gate, long long gate_stride, const T* __restrict__ weight, long long vectors,
-                      int heads, int V, float eps, float scale) {
+                      int heads, int V, float eps, float scale, int sigmoid_gate) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_GATED_NORM);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (long long n = (long long)blockIdx.x * (CP_THREADS / 32) + warp; n < vectors;
@@ -617,14 +689,15 @@ gated_rms_norm_kernel(T* __restrict__ out, long long out_stride, const float* __
     const float inv = scale / sqrtf(warp_sum(ss) / (float)V + eps);
     for (int i = lane; i < V; i += 32) {
       const float gv = to_float(g[i]);
-      dst[i] = from_float<T>(src[i] * inv * to_float(weight[i]) * (gv / (1.0f + expf(-gv))));
+      const float sig = 1.0f / (1.0f + expf(-gv));
+      dst[i] = from_float<T>(src[i] * inv * to_float(weight[i]) * (sigmoid_gate ? sig : gv * sig));
     }
   }
 }
 
 extern "C" int kvb_gated_rms_norm(void* out, long long out_stride, const float* o, const void* gate,
                                   long long gate_stride, const void* weight, int tokens, int heads, int V, float eps,
-                                  float scale, int dtype, cudaStream_t stream) {
+                                  float scale, int sigmoid_gate, int dtype, cudaStream_t stream) {
   const long long vectors = (long long)tokens * heads;
   if (vectors == 0) return 0;
   KVB_REQUIRE(V > 0, "gated_rms_norm: bad width");
@@ -633,10 +706,10 @@ extern "C" int kvb_gated_rms_norm(void* out, long long out_stride, const float* 
   const int blocks = (int)(wanted < resident ? wanted : resident);
   if (dtype == KVB_F32)
     KVB_CHECK_CUDA(kvb_launch((gated_rms_norm_kernel<float>), dim3(blocks), dim3(CP_THREADS), 0, stream, true,
-        (float*)out, out_stride, o, (const float*)gate, gate_stride, (const float*)weight, vectors, heads, V, eps, scale));
+        (float*)out, out_stride, o, (const float*)gate, gate_stride, (const float*)weight, vectors, heads, V, eps, scale, sigmoid_gate));
   else
     KVB_CHECK_CUDA(kvb_launch((gated_rms_norm_kernel<bf16>), dim3(blocks), dim3(CP_THREADS), 0, stream, true,
-        (bf16*)out, out_stride, o, (const bf16*)gate, gate_stride, (const bf16*)weight, vectors, heads, V, eps, scale));
+        (bf16*)out, out_stride, o, (const bf16*)gate, gate_stride, (const bf16*)weight, vectors, heads, V, eps, scale, sigmoid_gate));
   KVB_CHECK_LAUNCH();
   return 0;
 }

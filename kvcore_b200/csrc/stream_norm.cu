@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(SN_THREADS)
 stream_add_norm_kernel(float* out, const float* x, const T* __restrict__ a,
                        const W* __restrict__ weight, int width, float eps, float* __restrict__ avg,
                        const float* __restrict__ stack, long long stack_stride, const W* __restrict__ coeffs,
-                       int count) {
+                       int count, T* __restrict__ rounded) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_ADD_NORM);
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * width;
@@ -327,6 +327,12 @@ stream_add_norm_kernel(float* out, const float* x, const T* __restrict__ a,
 #pragma unroll
         for (int j = 0; j < 4; ++j) q.v[j] = stream[s][j];
         *reinterpret_cast<Quad4<float>*>(out + base + i) = q;
+        if (rounded != nullptr) {
+          Quad4<T> r;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) r.v[j] = from_float<T>(stream[s][j]);
+          *reinterpret_cast<Quad4<T>*>(rounded + base + i) = r;
+        }
       }
     }
     return;
@@ -368,7 +374,10 @@ stream_add_norm_kernel(float* out, const float* x, const T* __restrict__ a,
 #pragma unroll
     for (int s = 0; s < SN_KEEP; ++s) {
       const int i = threadIdx.x + s * SN_THREADS;
-      if (i < width) out[base + i] = stream[s];
+      if (i < width) {
+        out[base + i] = stream[s];
+        if (rounded != nullptr) rounded[base + i] = from_float<T>(stream[s]);
+      }
     }
     return;
   }
@@ -380,6 +389,7 @@ stream_add_norm_kernel(float* out, const float* x, const T* __restrict__ a,
   for (int i = threadIdx.x; i < width; i += SN_THREADS) {
     const float y = x[base + i] + to_float(arow[i]) * inv * to_float(weight[i]);
     out[base + i] = y;
+    if (rounded != nullptr) rounded[base + i] = from_float<T>(y);
     if (avg != nullptr) {
       float sum = 0.0f;
       for (int j = 0; j < count; ++j) sum = fmaf(to_float(coeffs[j]), stack[(size_t)j * stack_stride + base + i], sum);
@@ -390,7 +400,8 @@ stream_add_norm_kernel(float* out, const float* x, const T* __restrict__ a,
 
 extern "C" int kvb_stream_add_norm(float* out, const float* x, const void* a, const void* weight, int rows, int width,
                                    float eps, float* avg, const float* stack, long long stack_stride,
-                                   const void* coeffs, int count, int dtype, int weight_dtype, cudaStream_t stream) {
+                                   const void* coeffs, int count, void* rounded, int dtype, int weight_dtype,
+                                   cudaStream_t stream) {
   if (rows == 0) return 0;
   KVB_REQUIRE(width > 0, "stream_add_norm: width must be positive");
   KVB_REQUIRE(avg == nullptr || (coeffs != nullptr && count >= 0 && (count == 0 || stack != nullptr)),
@@ -398,16 +409,17 @@ extern "C" int kvb_stream_add_norm(float* out, const float* x, const void* a, co
   cudaError_t err;
   const bool kept = width <= SN_THREADS * SN_KEEP;
   const bool quads = kept && width % 4 == 0 && aligned16(out) && aligned16(x) && aligned16(a) && aligned16(weight) &&
+                     (rounded == nullptr || ((uintptr_t)rounded & 7) == 0) &&
                      (avg == nullptr || (aligned16(avg) && (count == 0 || (aligned16(stack) && stack_stride % 4 == 0))));
 #define KVB_AN_LAUNCH(T, W)                                                                                       \
   err = quads                                                                                                     \
       ? kvb_launch((stream_add_norm_kernel<T, W, 2>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x,     \
-                   (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count)  \
+                   (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count, (T*)rounded)  \
       : kept                                                                                                      \
       ? kvb_launch((stream_add_norm_kernel<T, W, 1>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x,     \
-                   (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count)  \
+                   (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count, (T*)rounded)  \
       : kvb_launch((stream_add_norm_kernel<T, W, 0>), dim3(rows), dim3(SN_THREADS), 0, stream, true, out, x,     \
-                   (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count)
+                   (const T*)a, (const W*)weight, width, eps, avg, stack, stack_stride, (const W*)coeffs, count, (T*)rounded)
   if (dtype == KVB_F32 && weight_dtype == KVB_F32) KVB_AN_LAUNCH(float, float);
   else if (dtype == KVB_F32) KVB_AN_LAUNCH(float, bf16);
   else if (weight_dtype == KVB_F32) KVB_AN_LAUNCH(bf16, float);

@@ -12,6 +12,13 @@
 //   the scale alone).
 //
 //   embed_scaled: the 32-bit stream's first value, table[id] * scale.
+//
+//   Two optional steps of turn_norm_kv_write: a query temperature, q times
+//   1 + coef * ln(floor((position + 1) / every) + 1); and value mixing, the cached values become
+//   (1 - lambda) v + lambda v_first with v_first another layer's values of the same token (rows of a tensor of
+//   their own) and lambda one 32-bit number.
+//
+//   gelu_mul: out[t, j] = gelu_tanh(z[t, j]) * rows[t, column + j].
 #include "common.cuh"
 
 #define TN_THREADS 128
@@ -23,12 +30,15 @@ turn_norm_kv_write_kernel(T* __restrict__ rows, long long row_stride, const floa
                           const int* __restrict__ positions, const int* __restrict__ req_index,
                           const int* __restrict__ table, int table_stride, T* __restrict__ cache, int page_size,
                           int num_pages, int write, int q_heads, int k_heads, int D, int v_width, int per_block,
-                          int* status) {
+                          float temp_coef, int temp_every, const T* __restrict__ mix_values, long long mix_stride,
+                          const float* __restrict__ mix_weight, int* status) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_TURN_NORM);
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   T* row = rows + (size_t)t * row_stride;
   const int pos = positions[t];
   const float fpos = (float)pos;
+  // the query temperature of this position (1 without one)
+  const float temperature = temp_every > 0 ? 1.0f + temp_coef * logf((float)((pos + 1) / temp_every + 1)) : 1.0f;
   T* dst = nullptr;
   if (write) {
     const int page = table[(size_t)req_index[t] * table_stride + pos / page_size];
@@ -62,7 +72,8 @@ turn_norm_kv_write_kernel(T* __restrict__ rows, long long row_stride, const floa
       ss = fmaf(u, u, ss);
       ss = fmaf(v, v, ss);
     }
-    const float inv = norm ? 1.0f / sqrtf(warp_sum(ss) / (float)D + eps) : 1.0f;
+    float inv = norm ? 1.0f / sqrtf(warp_sum(ss) / (float)D + eps) : 1.0f;
+    if (is_q) inv *= temperature;
     if (o == nullptr) continue;
     for (int pair = lane; pair < pairs; pair += 32) {
       const int e = 2 * pair;
@@ -83,7 +94,14 @@ turn_norm_kv_write_kernel(T* __restrict__ rows, long long row_stride, const floa
   if (dst != nullptr && blockIdx.y == 0) {
     const T* v = row + (size_t)(q_heads + k_heads) * D;
     T* out = dst + (size_t)k_heads * D;
-    for (int i = threadIdx.x; i < v_width; i += TN_THREADS) out[i] = v[i];
+    if (mix_values != nullptr) {
+      const float lam = mix_weight[0];
+      const T* first = mix_values + (size_t)t * mix_stride;
+      for (int i = threadIdx.x; i < v_width; i += TN_THREADS)
+        out[i] = from_float<T>((1.0f - lam) * to_float(v[i]) + lam * to_float(first[i]));
+    } else {
+      for (int i = threadIdx.x; i < v_width; i += TN_THREADS) out[i] = v[i];
+    }
   }
 }
 
@@ -91,10 +109,14 @@ extern "C" int kvb_turn_norm_kv_write(void* rows, long long row_stride, const fl
                                       const void* q_weight, const void* k_weight, int norm, float eps,
                                       const int* positions, const int* req_index, const int* table, int table_stride,
                                       void* cache, int page_size, int num_pages, int write, int tokens, int q_heads,
-                                      int k_heads, int D, int v_width, int dtype, cudaStream_t stream) {
+                                      int k_heads, int D, int v_width, float temp_coef, int temp_every,
+                                      const void* mix_values, long long mix_stride, const float* mix_weight,
+                                      int dtype, cudaStream_t stream) {
   if (tokens == 0) return 0;
   KVB_REQUIRE(q_heads > 0 && k_heads > 0 && D > 0 && v_width > 0, "turn_norm_kv_write: bad sizes");
   KVB_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= D, "turn_norm_kv_write: the turned entries are an even number within the head");
+  KVB_REQUIRE(temp_every >= 0 && (mix_values == nullptr || mix_weight != nullptr),
+              "turn_norm_kv_write: the temperature's period is not negative, and mixed values need their weight");
   int* status = kvb_status_word();
   KVB_REQUIRE(status != nullptr, "turn_norm_kv_write: no status word");
   const int vectors = q_heads + (write ? k_heads : 0);
@@ -105,12 +127,12 @@ extern "C" int kvb_turn_norm_kv_write(void* rows, long long row_stride, const fl
     KVB_CHECK_CUDA(kvb_launch((turn_norm_kv_write_kernel<float>), dim3(tokens, groups), dim3(TN_THREADS), 0, stream, true,
         (float*)rows, row_stride, inv_freq, rot, (const float*)q_weight, (const float*)k_weight, norm, eps, positions,
         req_index, table, table_stride, (float*)cache, page_size, num_pages, write, q_heads, k_heads, D, v_width,
-        per_block, status));
+        per_block, temp_coef, temp_every, (const float*)mix_values, mix_stride, mix_weight, status));
   else
     KVB_CHECK_CUDA(kvb_launch((turn_norm_kv_write_kernel<bf16>), dim3(tokens, groups), dim3(TN_THREADS), 0, stream, true,
         (bf16*)rows, row_stride, inv_freq, rot, (const bf16*)q_weight, (const bf16*)k_weight, norm, eps, positions,
         req_index, table, table_stride, (bf16*)cache, page_size, num_pages, write, q_heads, k_heads, D, v_width,
-        per_block, status));
+        per_block, temp_coef, temp_every, (const bf16*)mix_values, mix_stride, mix_weight, status));
   KVB_CHECK_LAUNCH();
   return 0;
 }
@@ -177,6 +199,42 @@ extern "C" int kvb_embed_scaled(float* out, const void* table, const int* ids, i
   else
     KVB_CHECK_CUDA(kvb_launch((embed_scaled_kernel<bf16>), dim3(tokens), dim3(threads), 0, stream, true, out,
         (const bf16*)table, ids, vocab, width, scale, status));
+  KVB_CHECK_LAUNCH();
+  return 0;
+}
+
+// out[t, j] = gelu_tanh(z[t, j]) * rows[t, column + j], gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))),
+// in 32-bit with one rounding at the store: the gate of an input that every token brings with it.
+template <typename T>
+__global__ void gelu_mul_kernel(T* __restrict__ out, const T* __restrict__ z, const T* __restrict__ rows,
+                                long long rows_stride, int column, long long count, int dim) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_GELU_MUL);
+  const long long step = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < count; i += step) {
+    const long long t = i / dim;
+    const int j = (int)(i - t * dim);
+    const float x = to_float(z[i]);
+    const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    const float gelu = 0.5f * x * (1.0f + tanhf(inner));
+    out[i] = from_float<T>(gelu * to_float(rows[t * rows_stride + column + j]));
+  }
+}
+
+extern "C" int kvb_gelu_mul(void* out, const void* z, const void* rows, long long rows_stride, int column, int tokens,
+                            int dim, int dtype, cudaStream_t stream) {
+  const long long count = (long long)tokens * dim;
+  if (count == 0) return 0;
+  KVB_REQUIRE(column >= 0 && dim > 0, "gelu_mul: bad sizes");
+  const int threads = 256;
+  const long long wanted = (count + threads - 1) / threads;
+  const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
+  const int blocks = (int)(wanted < resident ? wanted : resident);
+  if (dtype == KVB_F32)
+    KVB_CHECK_CUDA(kvb_launch((gelu_mul_kernel<float>), dim3(blocks), dim3(threads), 0, stream, true, (float*)out,
+        (const float*)z, (const float*)rows, rows_stride, column, count, dim));
+  else
+    KVB_CHECK_CUDA(kvb_launch((gelu_mul_kernel<bf16>), dim3(blocks), dim3(threads), 0, stream, true, (bf16*)out,
+        (const bf16*)z, (const bf16*)rows, rows_stride, column, count, dim));
   KVB_CHECK_LAUNCH();
   return 0;
 }

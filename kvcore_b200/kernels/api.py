@@ -51,7 +51,8 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_qk_prepare": [_vp, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp, _vp, _int, _int, _int, _int, _int,
                            _int, _int, _float, _int, _int, _int, _int, _vp],
         "kvb_glu_clamped": [_vp, _vp, _int, _int, _float, _float, _float, _int, _vp],
-        "kvb_moe_route": [_vp, _vp, _vp, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _vp],
+        "kvb_moe_route": [_vp, _vp, _vp, _vp, _ll, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _vp, _int, _int,
+                          _float, _int, _vp],
         "kvb_moe_align": [_vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _vp],
         "kvb_moe_gemv": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _int, _int, _int, _int, _int, _vp],
         "kvb_moe_gemv_rows": [_vp, _vp, _ll, _int, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _vp],
@@ -70,12 +71,12 @@ def ensure_built(verbose: bool = False) -> str:
                                   _int, _int, _int, _float, _int, _vp, _vp],
         "kvb_gemm_f32": [_vp, _vp, _vp, _vp, _int, _int, _int, _ll, _ll, _vp],
         "kvb_rms_norm_shift": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _float, _int, _int, _int, _vp],
-        "kvb_stream_add_norm": [_vp, _vp, _vp, _vp, _int, _int, _float, _vp, _vp, _ll, _vp, _int, _int, _int, _vp],
+        "kvb_stream_add_norm": [_vp, _vp, _vp, _vp, _int, _int, _float, _vp, _vp, _ll, _vp, _int, _vp, _int, _int, _vp],
         "kvb_attention_dims_rows": [_vp, _ll, _ll, _int, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp,
-                                    _int, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _float,
+                                    _int, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _float,
                                     _int, _int, _vp],
         "kvb_flash_dims_attention": [_vp, _ll, _ll, _int, _vp, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp,
-                                     _int, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _int,
+                                     _int, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _int, _int,
                                      _float, _int, _int, _vp, _vp],
         "kvb_latent_prepare": [_vp, _ll, _vp, _float, _vp, _int, _vp, _vp, _vp, _int, _vp, _int, _int, _int, _vp,
                                _ll, _ll, _int, _vp, _ll, _ll, _vp, _int, _int, _int, _int, _int, _int, _vp],
@@ -92,9 +93,12 @@ def ensure_built(verbose: bool = False) -> str:
         "kvb_delta_scan": [_vp, _vp, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _int, _int, _vp],
         "kvb_conv_prepare": [_vp, _vp, _ll, _vp, _int, _vp, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int,
                              _int, _int, _int, _int, _float, _float, _int, _vp],
-        "kvb_gated_rms_norm": [_vp, _ll, _vp, _vp, _ll, _vp, _int, _int, _int, _float, _float, _int, _vp],
+        "kvb_gated_rms_norm": [_vp, _ll, _vp, _vp, _ll, _vp, _int, _int, _int, _float, _float, _int, _int, _vp],
+        "kvb_lightning_scan": [_vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp, _ll, _ll, _vp, _vp, _int, _int, _int, _int, _int,
+                               _float, _int, _vp],
+        "kvb_gelu_mul": [_vp, _vp, _vp, _ll, _int, _int, _int, _int, _vp],
         "kvb_turn_norm_kv_write": [_vp, _ll, _vp, _int, _vp, _vp, _int, _float, _vp, _vp, _vp, _int, _vp, _int, _int,
-                                   _int, _int, _int, _int, _int, _int, _int, _vp],
+                                   _int, _int, _int, _int, _int, _int, _float, _int, _vp, _ll, _vp, _int, _vp],
         "kvb_head_gate": [_vp, _ll, _vp, _vp, _ll, _int, _int, _int, _float, _int, _vp],
         "kvb_embed_scaled": [_vp, _vp, _vp, _int, _int, _int, _float, _int, _vp],
         "kvb_sample": [_vp, _vp, _vp, _int, _int, _float, _vp],
@@ -669,7 +673,7 @@ _stream_scratch: dict[int, torch.Tensor] = {}
 TRACE_TAGS = {27: "rms_norm_shift", 28: "stream_add_norm", 29: "attention_dims_rows", 30: "latent_prepare",
               31: "head_norm_kv_write", 32: "maps_combine", 33: "sigmoid_gate_mul", 34: "flash_dims",
               35: "flash_dims_combine", 36: "gather_cached_rows", 37: "gla_scan", 38: "delta_scan", 39: "conv_prepare",
-              40: "gated_rms_norm", 41: "turn_norm_kv_write", 42: "head_gate", 43: "embed_scaled", 44: "gla_prepare", 25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
+              40: "gated_rms_norm", 41: "turn_norm_kv_write", 42: "head_gate", 43: "embed_scaled", 44: "gla_prepare", 45: "gelu_mul", 46: "lightning_prepare", 47: "lightning_scan", 25: "kept_first_merge", 26: "moe_gather", 17: "layer_norm", 18: "stream_add", 19: "qk_prepare", 20: "glu_clamped", 21: "moe_route",
               22: "moe_align", 23: "moe_gemm", 24: "moe_combine", 1: "gather_rows", 2: "rmsnorm", 3: "silu_mul", 4: "rope_table", 5: "rope_kv_write", 6: "attention_rows",
               7: "flash_paged", 8: "flash_combine", 9: "flash_decode_tma", 10: "flash_decode_combine",
               11: "flash_prefill_tc5", 12: "gemm_f32", 13: "gemm_stream", 14: "sample", 16: "feed_tokens"}
@@ -991,11 +995,13 @@ def rms_norm_shift(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype:
 
 def stream_add_norm(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float, *,
                     out: torch.Tensor | None = None, stack: torch.Tensor | None = None, depth: int = 0,
-                    coeffs: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+                    coeffs: torch.Tensor | None = None, rounded: torch.dtype | None = None) -> tuple:
     """``X = x + a * rsqrt(mean(a^2) + eps) * weight`` on the 32-bit stream ``x [rows, width]`` (``a``: a
     sub-layer's output), into ``out`` (default: in place).  With ``coeffs`` (``[depth + 1]``) it also returns
     the weighted average ``sum_{j < depth} coeffs[j] * stack[j] + coeffs[depth] * X`` over the results in
-    front (``stack [>= depth, rows, width]`` 32-bit); returns ``(X, average or None)``."""
+    front (``stack [>= depth, rows, width]`` 32-bit); returns ``(X, average or None)``.  With ``rounded``
+    (the type of ``a``) it also leaves ``X`` in that type, for a matrix product that reads the stream itself,
+    and returns ``(X, average or None, X in that type)``."""
     _check(x, "x", dtype=torch.float32)
     _check(a, "a")
     _check(weight, "weight")
@@ -1020,9 +1026,15 @@ def stream_add_norm(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps:
                 raise KernelError(f"stream_add_norm: stack {tuple(stack.shape)} does not hold {depth} x {tuple(x.shape)}")
         avg = torch.empty_like(x)
         extra = (avg.data_ptr(), None if not depth else stack.data_ptr(), rows * width, coeffs.data_ptr(), depth)
+    narrow = None
+    if rounded is not None:
+        if rounded != a.dtype:
+            raise KernelError(f"stream_add_norm: the stream is also left in the type of a ({a.dtype}), not {rounded}")
+        narrow = torch.empty(x.shape, dtype=rounded, device=x.device)
     _call("kvb_stream_add_norm", out.data_ptr(), x.data_ptr(), a.data_ptr(), weight.data_ptr(), rows, width,
-          float(eps), *extra, _dtype_code(a), _dtype_code(weight), _stream())
-    return out, avg
+          float(eps), *extra, None if narrow is None else narrow.data_ptr(), _dtype_code(a), _dtype_code(weight),
+          _stream())
+    return (out, avg) if rounded is None else (out, avg, narrow)
 
 
 def attention_dims(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, table: torch.Tensor, ctx, *,
@@ -1030,7 +1042,8 @@ def attention_dims(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, ta
                    num_pages: int, key_strides: tuple[int, int, int], value_strides: tuple[int, int, int], scale: float,
                    sink: torch.Tensor | None = None, window: int | None = None,
                    out: torch.Tensor | None = None, out_dtype: torch.dtype | None = None,
-                   force_general: bool = False, num_splits: int | None = None) -> torch.Tensor:
+                   force_general: bool = False, num_splits: int | None = None,
+                   slopes: torch.Tensor | None = None) -> torch.Tensor:
     """Paged attention with a key width and a value width of their own.
 
     ``q [T, HQ, key_width]`` (a view; last stride 1) with ``HQ = value_heads * group * maps``: query head
@@ -1038,7 +1051,8 @@ def attention_dims(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, ta
     ``values`` are tensors inside the paged cache (they may be views of one plane, and ``values`` may be a
     view of ``keys``); ``key_strides`` / ``value_strides`` give their (page, head, row) strides in elements;
     page ``p`` slot ``s`` head ``h`` starts at ``p * page + h * head + s * row``.  ``sink [HQ]`` (32-bit):
-    a logit per query head that joins the softmax's denominator.  Returns ``[T, HQ, value_width]`` in
+    a logit per query head that joins the softmax's denominator.  ``slopes [HQ]`` (32-bit): query head ``hq``'s
+    score of the key at position ``j`` for the query at position ``i`` is lowered by ``slopes[hq] * (i - j)``.  Returns ``[T, HQ, value_width]`` in
     ``out_dtype`` (32-bit or the cache's type; default the cache's) or fills ``out`` (a view with last
     stride 1).  bfloat16 shapes the tensor-core kernel takes run there; everything else, and all of float32,
     on the general kernel."""
@@ -1058,18 +1072,23 @@ def attention_dims(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, ta
         _check(sink, "sink", dtype=torch.float32)
         if sink.numel() != hq:
             raise KernelError(f"attention_dims: {sink.numel()} sinks for {hq} query heads")
+    if slopes is not None:
+        _check(slopes, "slopes", dtype=torch.float32)
+        if slopes.numel() != hq:
+            raise KernelError(f"attention_dims: {slopes.numel()} slopes for {hq} query heads")
     if tokens == 0:
         return out
     if (not force_general and flash_dims_supported(q, out, key_width, value_width, page_size, key_strides,
                                                     value_strides, keys, values, maps)):
         _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_width, value_width, page_size,
-                    num_pages, key_strides, value_strides, scale, sink, window, num_splits)
+                    num_pages, key_strides, value_strides, scale, sink, window, num_splits, slopes)
         return out
     _call("kvb_attention_dims_rows", out.data_ptr(), out.stride(0), out.stride(1), int(out.dtype == torch.float32),
           q.data_ptr(), q.stride(0), q.stride(1), keys.data_ptr(), *key_strides, values.data_ptr(), *value_strides,
           table.data_ptr(), table.stride(0), ctx.positions.data_ptr(), ctx.req_index.data_ptr(),
-          None if sink is None else sink.data_ptr(), tokens, hq, group * maps, maps, key_width, value_width,
-          page_size, num_pages, float(scale), int(window or 0), _dtype_code(q), _stream())
+          None if sink is None else sink.data_ptr(), None if slopes is None else slopes.data_ptr(), tokens, hq,
+          group * maps, maps, key_width, value_width, page_size, num_pages, float(scale), int(window or 0),
+          _dtype_code(q), _stream())
     return out
 
 
@@ -1116,7 +1135,7 @@ def flash_dims_supported(q, out, key_width, value_width, page_size, key_strides,
 
 
 def _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_width, value_width, page_size,
-                num_pages, key_strides, value_strides, scale, sink, window, num_splits) -> None:
+                num_pages, key_strides, value_strides, scale, sink, window, num_splits, slopes=None) -> None:
     """The tensor-core kernel on the step's batch.  A mixed step (portions of prompts beside single decoded
     tokens, longest first as the step function packs them) goes as two runs of requests, so that the
     decoded tokens take the shape made for few rows and have their keys cut into chunks."""
@@ -1158,7 +1177,7 @@ def _flash_dims(out, q, keys, values, table, ctx, value_heads, group, maps, key_
               int(out.dtype == torch.float32), q.data_ptr(), q.stride(0), q.stride(1), keys.data_ptr(), *key_strides,
               values.data_ptr(), *value_strides, run_table.data_ptr(), run_table.stride(0),
               run.query_start.data_ptr(), run.context_lens.data_ptr(), None if sink is None else sink.data_ptr(),
-              run.num_reqs, run.max_query_len, value_heads, group, maps, key_width, value_width, page_size,
+              None if slopes is None else slopes.data_ptr(), run.num_reqs, run.max_query_len, value_heads, group, maps, key_width, value_width, page_size,
               num_pages, float(scale), int(window or 0), splits, None if scratch is None else scratch.data_ptr(),
               _stream(), kernels=2 if splits > 1 else 1)
 
@@ -1321,13 +1340,17 @@ def embed_scaled(table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.
 def turn_norm_kv_write(rows: torch.Tensor, inv_freq: torch.Tensor | None, rot: int, ctx, table: torch.Tensor,
                        cache: torch.Tensor, *, q_heads: int, k_heads: int, dim: int, value_width: int,
                        norm: bool = True, eps: float = 0.0, q_weight: torch.Tensor | None = None,
-                       k_weight: torch.Tensor | None = None, write: bool = True) -> None:
+                       k_weight: torch.Tensor | None = None, write: bool = True, q_temp: tuple | None = None,
+                       mix_values: torch.Tensor | None = None, mix_weight: torch.Tensor | None = None) -> None:
     """q ``[q_heads, dim]`` and k ``[k_heads, dim]`` at the start of each row of ``rows`` (a view; last stride 1),
     then ``value_width`` value entries.  The first ``rot`` entries of every head turn in neighbouring pairs
     (2i, 2i+1) by ``position * inv_freq[i]``; then (``norm``) every head is divided by
-    ``sqrt(mean(x^2) + eps)`` (times ``q_weight`` / ``k_weight [dim]`` when given).  q is replaced in place;
+    ``sqrt(mean(x^2) + eps)`` (times ``q_weight`` / ``k_weight [dim]`` when given).  ``q_temp = (coef, every)``:
+    q is then multiplied by ``1 + coef * ln(floor((position + 1) / every) + 1)``.  q is replaced in place;
     with ``write`` the keys and the values go side by side into the token's row of ``cache``
-    ``[pages, 1, page, k_heads * dim + value_width]``."""
+    ``[pages, 1, page, k_heads * dim + value_width]``; with ``mix_values [T, value_width]`` (a view) and
+    ``mix_weight`` (one 32-bit number ``lambda``) the cached values are
+    ``(1 - lambda) * values + lambda * mix_values``."""
     _check(rows, "rows", contiguous=False)
     _check(cache, "cache", dtype=rows.dtype)
     _check(table, "block table", dtype=torch.int32, contiguous=False)
@@ -1348,11 +1371,23 @@ def turn_norm_kv_write(rows: torch.Tensor, inv_freq: torch.Tensor | None, rot: i
     if one != 1 or width != k_heads * dim + value_width or table.stride(1) != 1:
         raise KernelError(f"turn_norm_kv_write: cache {tuple(cache.shape)} does not hold rows of "
                           f"{k_heads} x {dim} + {value_width}")
+    if q_temp is not None and int(q_temp[1]) <= 0:
+        raise KernelError(f"turn_norm_kv_write: the temperature's period must be positive, got {q_temp[1]}")
+    if mix_values is not None:
+        _check(mix_values, "mix_values", dtype=rows.dtype, contiguous=False)
+        if tuple(mix_values.shape) != (tokens, value_width) or (tokens and mix_values.stride(1) != 1):
+            raise KernelError(f"turn_norm_kv_write: values to mix in {tuple(mix_values.shape)} are not "
+                              f"[{tokens}, {value_width}]")
+        if mix_weight is None:
+            raise KernelError("turn_norm_kv_write: values to mix in need their weight")
+        _check(mix_weight, "mix_weight", dtype=torch.float32)
     _call("kvb_turn_norm_kv_write", rows.data_ptr(), rows.stride(0), None if not rot else inv_freq.data_ptr(), rot,
           None if q_weight is None else q_weight.data_ptr(), None if k_weight is None else k_weight.data_ptr(),
           int(bool(norm)), float(eps), ctx.positions.data_ptr(), ctx.req_index.data_ptr(), table.data_ptr(),
           table.stride(0), cache.data_ptr(), page_size, num_pages, int(bool(write)), tokens, q_heads, k_heads, dim,
-          value_width, _dtype_code(rows), _stream())
+          value_width, 0.0 if q_temp is None else float(q_temp[0]), 0 if q_temp is None else int(q_temp[1]),
+          None if mix_values is None else mix_values.data_ptr(), 0 if mix_values is None else mix_values.stride(0),
+          None if mix_values is None else mix_weight.data_ptr(), _dtype_code(rows), _stream())
 
 
 def head_gate(o: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
@@ -1454,9 +1489,13 @@ def delta_scan(prepared: torch.Tensor, state: torch.Tensor, ctx, *, heads: int, 
 
 
 def gated_rms_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-                   scale: float = 1.0) -> torch.Tensor:
+                   scale: float = 1.0, *, gate_act: str = "silu") -> torch.Tensor:
     """``out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]) * scale``:
-    ``o [T, H, V]`` 32-bit, ``gate`` and ``out [T, H * V]`` views of the activation type, ``weight [V]``."""
+    ``o [T, H, V]`` 32-bit, ``gate`` and ``out [T, H * V]`` views of the activation type, ``weight [V]``.
+    ``gate_act="sigmoid"``: ``sigmoid(gate)`` in place of ``silu(gate)``.  (A norm over all heads together is
+    the case ``H = 1``.)"""
+    if gate_act not in ("silu", "sigmoid"):
+        raise KernelError(f"gated_rms_norm: the gate passes silu or sigmoid, not {gate_act!r}")
     _check(o, "o", dtype=torch.float32)
     _check(gate, "gate", contiguous=False)
     _check(out, "out", dtype=gate.dtype, contiguous=False)
@@ -1467,7 +1506,52 @@ def gated_rms_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, ep
         raise KernelError(f"gated_rms_norm: gate {tuple(gate.shape)} / out {tuple(out.shape)} / weight do not fit "
                           f"o {tuple(o.shape)}")
     _call("kvb_gated_rms_norm", out.data_ptr(), out.stride(0), o.data_ptr(), gate.data_ptr(), gate.stride(0),
-          weight.data_ptr(), tokens, heads, width, float(eps), float(scale), _dtype_code(out), _stream())
+          weight.data_ptr(), tokens, heads, width, float(eps), float(scale), int(gate_act == "sigmoid"),
+          _dtype_code(out), _stream())
+    return out
+
+
+def lightning_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, ctx, *,
+                   heads: int, dim: int, value_dim: int, q_scale: float = 1.0, state_offset: int = 0) -> torch.Tensor:
+    """Linear attention with one fixed decay a head over the step's tokens, request by request in order:
+    ``S <- decay[h] S + k_t v_t^T``, ``o_t = S^T q_t`` with ``q_t = silu(q) * q_scale``, ``k_t = silu(k)``,
+    ``v_t = silu(v)``.  ``q, k [T, heads * dim]`` and ``v [T, heads * value_dim]`` are views of one tensor of
+    projected rows, ``decay [heads]`` 32-bit; ``state [slots, n]`` (32-bit) holds each request's ``S`` column by
+    column (``[heads, value_dim, dim]``) at ``state_offset`` of its slot's row and is brought up to date.
+    Returns ``o [T, heads, value_dim]`` 32-bit."""
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _check(t, name, dtype=q.dtype, contiguous=False)
+        if t.stride(1) != 1 or t.shape[0] != q.shape[0]:
+            raise KernelError(f"lightning_scan: {name} {tuple(t.shape)} is not a view of the step's rows")
+    if q.stride(0) != k.stride(0) or q.stride(0) != v.stride(0):
+        raise KernelError("lightning_scan: q, k and v must be views of one tensor of rows")
+    if q.shape[1] != heads * dim or k.shape[1] != heads * dim or v.shape[1] != heads * value_dim:
+        raise KernelError("lightning_scan: widths do not match the head layout")
+    _check(decay, "decay", dtype=torch.float32)
+    if decay.numel() != heads:
+        raise KernelError(f"lightning_scan: {decay.numel()} decays for {heads} heads")
+    _state_row(state, state_offset, heads * dim * value_dim)
+    out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
+    # what the scan reads a token, 32-bit: silu(q) times its scale, silu(k)
+    prepared = torch.empty((q.shape[0], 2 * heads * dim), dtype=torch.float32, device=q.device)
+    _call("kvb_lightning_scan", out.data_ptr(), prepared.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+          q.stride(0), decay.data_ptr(), state.data_ptr(), state.stride(0), state_offset, ctx.query_start.data_ptr(),
+          ctx.state_slots.data_ptr(), q.shape[0], ctx.num_reqs, heads, dim, value_dim, float(q_scale),
+          _dtype_code(q), _stream(), kernels=2)
+    return out
+
+
+def gelu_mul(z: torch.Tensor, rows: torch.Tensor, column: int) -> torch.Tensor:
+    """``gelu_tanh(z) * rows[:, column:column + dim]`` for ``z [T, dim]``, in 32-bit with one rounding;
+    ``rows [T, n]`` of the same type (a table's rows of the step's tokens)."""
+    _check(z, "z")
+    _check(rows, "rows", dtype=z.dtype, contiguous=False)
+    tokens, dim = z.shape
+    if rows.dim() != 2 or rows.shape[0] != tokens or column < 0 or column + dim > rows.shape[1] or rows.stride(1) != 1:
+        raise KernelError(f"gelu_mul: rows {tuple(rows.shape)} have no columns [{column}, {column + dim}) for z {tuple(z.shape)}")
+    out = torch.empty_like(z)
+    _call("kvb_gelu_mul", out.data_ptr(), z.data_ptr(), rows.data_ptr(), rows.stride(0), int(column), tokens, dim,
+          _dtype_code(z), _stream())
     return out
 
 
@@ -1544,9 +1628,13 @@ MOE_SCORE_MODES = {"sigmoid": 0, "softmax": 1}
 
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, top: int, *, score: str = "sigmoid", renormalize: bool = False,
-              gate_rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
+              gate_rows: torch.Tensor | None = None, correction: torch.Tensor | None = None, group_count: int = 1,
+              group_keep: int = 1, weight_scale: float = 1.0) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor | None]:
     """Router of a mixture of experts on ``x [T, K]``: 32-bit logits with the 32-bit matrix ``router [E, K]``,
-    scores by ``score``, the ``top`` largest per token.  Returns ``(ids [T, top] int32, weights [T, top] float32,
+    scores by ``score``, the ``top`` largest per token.  ``correction [E]`` (32-bit): the choice goes by
+    ``score + correction``, the weights stay the scores.  ``group_count`` / ``group_keep``: the experts form
+    equal groups of neighbours, a group's score is its largest choice score, and only experts of the
+    ``group_keep`` best groups can be chosen.  ``weight_scale`` multiplies the weights.  Returns ``(ids [T, top] int32, weights [T, top] float32,
     gates)``; ``gates [T, R]`` = ``sigmoid(gate_rows @ x)`` for the 32-bit rows ``gate_rows [R, K]``, else None."""
     _check(x, "x", contiguous=False)
     _check(router, "router", dtype=torch.float32)
@@ -1563,9 +1651,18 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, top: int, *, score: str = "
             raise KernelError(f"moe_route: gate rows {tuple(gate_rows.shape)} do not match x")
         extra = gate_rows.shape[0]
         gates = torch.empty((tokens, extra), dtype=torch.float32, device=x.device)
+    if correction is not None:
+        _check(correction, "correction", dtype=torch.float32)
+        if correction.numel() != experts:
+            raise KernelError(f"moe_route: {correction.numel()} corrections for {experts} experts")
+    if (group_count <= 0 or experts % group_count or not 0 < group_keep <= group_count
+            or group_keep * (experts // group_count) < top):
+        raise KernelError(f"moe_route: {group_keep} of {group_count} groups of {experts} experts must hold {top} experts")
     _call("kvb_moe_route", ids.data_ptr(), weights.data_ptr(), None if gates is None else gates.data_ptr(),
           x.data_ptr(), x.stride(0), router.data_ptr(), None if gate_rows is None else gate_rows.data_ptr(),
-          tokens, experts, extra, k, int(top), MOE_SCORE_MODES[score], int(bool(renormalize)), _dtype_code(x), _stream())
+          tokens, experts, extra, k, int(top), MOE_SCORE_MODES[score], int(bool(renormalize)),
+          None if correction is None else correction.data_ptr(), int(group_count), int(group_keep), float(weight_scale),
+          _dtype_code(x), _stream())
     return ids, weights, gates
 
 

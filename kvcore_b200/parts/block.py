@@ -143,11 +143,18 @@ class SandwichResidualBlock(Block):
       ``sum_j c[j] * X_j + c[depth] * X``.  The results of a step live in one ``[depth_slots, T, width]``
       32-bit tensor shared through the step's context.
 
+    * ``token_side`` (``dict(dim, index, eps, scale, name)``): behind the last sub-layer the layer adds an input
+      of the token itself.  The model's embedding holds a side table with ``dim`` entries per token and layer;
+      with ``e`` this layer's entries (columns ``[index * dim, (index + 1) * dim)`` of the token's row),
+      ``y = P (gelu_tanh(G x) * e)`` reads the stream ``x`` itself, and
+      ``x <- x + scale * y * rsqrt(mean(y^2) + eps) * w``.  Tensors ``<name>.gate`` (``G [dim, width]``),
+      ``<name>.proj`` (``P [width, dim]``) and ``<name>.norm`` (``w [width]``).
+
     In the ``(h, residual)`` pair that runs through the blocks this block returns ``(Summed, stream)``."""
 
     def __init__(self, *, layer: LayerSpec, hidden_size: int, token_shift: str | None = None,
                  depth_average: str | None = None, depth: int = 0, depth_slots: int = 0,
-                 dtype: torch.dtype, device: torch.device) -> None:
+                 token_side: dict | None = None, dtype: torch.dtype, device: torch.device) -> None:
         self.hidden_size = int(hidden_size)
         self.dtype = dtype
         norms = layer.norms
@@ -171,6 +178,19 @@ class SandwichResidualBlock(Block):
                 raise ValueError(f"a depth average over {self.depth} results in front needs 0 < depth < depth_slots "
                                  f"({self.depth_slots})")
             self.average = torch.empty(self.depth + 1, dtype=dtype, device=device)
+        self.side = None
+        if token_side:
+            side = dict(token_side)
+            dim = int(side["dim"])
+            if dim <= 0 or int(side["index"]) < 0:
+                raise ValueError(f"a token side input needs a positive size and a place in the table, got {side}")
+            self.side = dict(dim=dim, column=int(side["index"]) * dim, eps=float(side["eps"]),
+                             scale=float(side.get("scale", 1.0)), name=side["name"])
+            self.side_gate = torch.empty(dim, self.hidden_size, dtype=dtype, device=device)
+            self.side_proj = torch.empty(self.hidden_size, dim, dtype=dtype, device=device)
+            self.side_norm = torch.empty(self.hidden_size, dtype=dtype, device=device)
+            # the norm's weight times the factor of the sum, formed once in 32-bit
+            self.side_factor = torch.empty(self.hidden_size, dtype=torch.float32, device=device)
 
     def parts(self):
         return tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.feed_forward_norm,
@@ -178,7 +198,11 @@ class SandwichResidualBlock(Block):
 
     graph_safe = PreNormResidualBlock.graph_safe
     ignorable_tensor_names = PreNormResidualBlock.ignorable_tensor_names
-    finalize_weights = PreNormResidualBlock.finalize_weights
+
+    def finalize_weights(self) -> None:
+        PreNormResidualBlock.finalize_weights(self)
+        if self.side is not None:
+            self.side_factor.copy_(self.side_norm.to(torch.float32) * self.side["scale"])
 
     def weight_slots(self) -> list[WeightSlot]:
         slots = PreNormResidualBlock.weight_slots(self)
@@ -186,6 +210,10 @@ class SandwichResidualBlock(Block):
             slots.append(WeightSlot(self.shift_tensor, self.shift, init="normal"))
         if self.average is not None:
             slots.append(WeightSlot(self.average_tensor, self.average, init="normal"))
+        if self.side is not None:
+            name = self.side["name"]
+            slots += [WeightSlot(f"{name}.gate", self.side_gate), WeightSlot(f"{name}.proj", self.side_proj),
+                      WeightSlot(f"{name}.norm", self.side_norm, init="ones")]
         return slots
 
     def state_spec(self) -> StateSpec | None:
@@ -209,20 +237,40 @@ class SandwichResidualBlock(Block):
         y = K.rms_norm_shift(x, weight, eps, self.dtype, shift=self.shift,
                              state=None if self.shift is None else cache.block_state, ctx=ctx)
         a = self.mixer.forward(y, ctx, cache)
-        weight, eps = self.mixer_out_norm.as_rms_scale()
-        # the layer's result goes to its place among the results when they are averaged; the stream handed
-        # in is then left as it was (it may be a result itself)
+        # The sums behind the sub-layers (and behind the token side input), in order: the last one is the layer's
+        # result.  It goes to its place among the results when they are averaged; the stream handed in is then
+        # left as it was (it may be a result itself).  The sum in front of a token side input also leaves the
+        # new stream in the activation type, for the side input's first product.
         place = None if stack is None else stack[self.depth]
         average = dict(stack=stack, depth=self.depth, coeffs=self.average) if stack is not None else {}
-        if self.feed_forward is None:
-            result, mean = K.stream_add_norm(x, a, weight, eps, out=place, **average)
-            return Summed(None), (result if mean is None else mean)
-        x, _ = K.stream_add_norm(x, a, weight, eps, out=place)
-        weight, eps = self.feed_forward_norm.as_rms_scale()
-        f = self.feed_forward.forward(K.rms_norm_shift(x, weight, eps, self.dtype), ctx)
-        weight, eps = self.feed_forward_out_norm.as_rms_scale()
-        result, mean = K.stream_add_norm(x, f, weight, eps, **average)
-        return Summed(None), (result if mean is None else mean)
+        narrow = self.dtype if self.side is not None and self.dtype != torch.float32 else None
+
+        def add(x, a, scale, last_sub_layer: bool):
+            weight, eps = scale
+            if last_sub_layer and self.side is None:
+                result, mean = K.stream_add_norm(x, a, weight, eps, out=place, **average)
+                return (result if mean is None else mean), None
+            if last_sub_layer and narrow is not None:
+                result, _, rounded = K.stream_add_norm(x, a, weight, eps, out=place, rounded=narrow)
+                return result, rounded
+            result, _ = K.stream_add_norm(x, a, weight, eps, out=place)
+            return result, None
+
+        x, rounded = add(x, a, self.mixer_out_norm.as_rms_scale(), self.feed_forward is None)
+        if self.feed_forward is not None:
+            weight, eps = self.feed_forward_norm.as_rms_scale()
+            f = self.feed_forward.forward(K.rms_norm_shift(x, weight, eps, self.dtype), ctx)
+            x, rounded = add(x, f, self.feed_forward_out_norm.as_rms_scale(), True)
+        if self.side is not None:
+            rows = ctx.shared("token_side_rows", lambda: None)
+            if rows is None:
+                raise RuntimeError(f"{self.side['name']}: the model's embedding has no side table")
+            z = K.linear(x if rounded is None else rounded, self.side_gate)
+            g = K.gelu_mul(z, rows, self.side["column"])
+            y = K.linear(g, self.side_proj)
+            result, mean = K.stream_add_norm(x, y, self.side_factor, self.side["eps"], **average)
+            x = result if mean is None else mean
+        return Summed(None), x
 
 
 BLOCKS.register("prenorm_residual", PreNormResidualBlock)

@@ -17,7 +17,8 @@ class TokenEmbedding(Part):
     graph_safe = True
 
     def __init__(self, *, vocab_size: int, hidden_size: int, name: str, tensor: str | None = None,
-                 scale: float | None = None, dtype, device) -> None:
+                 scale: float | None = None, side_tensor: str | None = None, side_width: int = 0,
+                 dtype, device) -> None:
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
         self.name = name
@@ -26,14 +27,28 @@ class TokenEmbedding(Part):
         self.scale = None if scale is None else float(scale)
         self.tensor = tensor or f"{name}.weight"     # the table's full checkpoint name
         self.weight = torch.empty(self.vocab_size, self.hidden_size, dtype=dtype, device=device)
+        # ``side_tensor``: a second table ``[vocab, side_width]`` whose row of a token is an input of the
+        # layers themselves (each block reads its own columns); gathered once a step by ``side_rows``
+        self.side_tensor, self.side_width = side_tensor, int(side_width)
+        if (side_tensor is None) != (self.side_width == 0):
+            raise ValueError("a side table needs both its tensor's name and its width")
+        self.side_weight = (torch.empty(self.vocab_size, self.side_width, dtype=dtype, device=device)
+                            if side_tensor is not None else None)
 
     def weight_slots(self) -> list[WeightSlot]:
-        return [WeightSlot(self.tensor, self.weight)]
+        slots = [WeightSlot(self.tensor, self.weight)]
+        if self.side_weight is not None:
+            slots.append(WeightSlot(self.side_tensor, self.side_weight))
+        return slots
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         if self.scale is not None:
             return K.embed_scaled(self.weight, token_ids, self.scale)
         return K.gather_rows(self.weight, token_ids)
+
+    def side_rows(self, token_ids: torch.Tensor) -> torch.Tensor | None:
+        """The step's rows ``[T, side_width]`` of the side table (None without one)."""
+        return None if self.side_weight is None else K.gather_rows(self.side_weight, token_ids)
 
 
 class LMHead(Part):

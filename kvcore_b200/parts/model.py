@@ -109,6 +109,10 @@ class DecoderModel:
         """Run the step's tokens through every schedule entry; returns ``(h, residual)``."""
         h = self.embedding.forward(ctx.token_ids)
         residual = None
+        # per-token inputs of the layers themselves: gathered once, every block reads its own columns
+        side_rows = getattr(self.embedding, "side_rows", None)
+        if side_rows is not None and getattr(self.embedding, "side_weight", None) is not None:
+            ctx.shared("token_side_rows", lambda: side_rows(ctx.token_ids))
         for index, entry in enumerate(self.schedule):
             h, residual = self.blocks[entry.layer].forward(h, residual, ctx, caches[index])
         return h, residual

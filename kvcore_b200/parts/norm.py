@@ -76,21 +76,33 @@ class LayerNorm(Norm):
 class RMSNormStream(Norm):
     """``x * rsqrt(mean(x^2) + eps) * weight`` over rows of a 32-bit residual stream (or of the activation
     type), written in the activation type; statistics and scaling in 32-bit.  ``tensor`` is the weight's full
-    checkpoint name (default ``<name>.weight``)."""
+    checkpoint name (default ``<name>.weight``).
+
+    ``offset`` and ``multiplier``: the factor is ``(stored + offset) * multiplier`` for the tensor ``stored`` of
+    the checkpoint (a weight stored around zero has ``offset`` 1; a norm whose result enters a sum with a
+    constant factor carries it as ``multiplier``).  The factor is then formed once, in 32-bit, and stays 32-bit
+    whatever the activation type: ``1 + w`` has more digits than the stored ``w``."""
 
     graph_safe = True
 
-    def __init__(self, *, size: int, eps: float, name: str, tensor: str | None = None,
-                 dtype: torch.dtype, device: torch.device):
+    def __init__(self, *, size: int, eps: float, name: str, tensor: str | None = None, offset: float = 0.0,
+                 multiplier: float = 1.0, dtype: torch.dtype, device: torch.device):
         self.size = int(size)
         self.eps = float(eps)
         self.name = name
         self.dtype = dtype
         self.tensor = tensor or f"{name}.weight"
-        self.weight = torch.empty(self.size, dtype=dtype, device=device)
+        self.offset, self.multiplier = float(offset), float(multiplier)
+        self.derived = self.offset != 0.0 or self.multiplier != 1.0
+        self.stored = torch.empty(self.size, dtype=dtype, device=device)
+        self.weight = torch.empty(self.size, dtype=torch.float32, device=device) if self.derived else self.stored
 
     def weight_slots(self) -> list[WeightSlot]:
-        return [WeightSlot(self.tensor, self.weight, init="ones")]
+        return [WeightSlot(self.tensor, self.stored, init="zeros" if self.offset == 1.0 else "ones")]
+
+    def finalize_weights(self) -> None:
+        if self.derived:
+            self.weight.copy_((self.stored.to(torch.float32) + self.offset) * self.multiplier)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return K.rms_norm_shift(x, self.weight, self.eps, self.dtype)

@@ -17,6 +17,10 @@ convolution over time and SiLU; q and k become unit vectors (q times ``dim^(-1/2
 multiplied by ``silu(W_g x)``.  The state of a request is ``S`` and the last ``taps - 1`` inputs of the
 convolution.  Both mixers keep ``S`` column by column (``[heads, value_dim, head_dim]``).
 
+``LightningAttention``: per head ``S_t = a S_{t-1} + k_t v_t^T``, ``o_t = S_t^T q_t`` with one fixed decay
+``a`` a head (a constant of the model) and ``q``, ``k``, ``v`` passed through SiLU; the heads' read-outs are
+RMS-normed together (one weight over all heads' values) and multiplied by ``sigmoid(W_g x)``.
+
 Decays, step sizes, unit norms, the state, the read-out and the norm behind it are 32-bit whatever the
 activation type.
 """
@@ -48,6 +52,7 @@ class ProjectedMixer(Mixer):
     in_rows: int
     out_cols: int
     state_offset = 0
+    in_bias = None            # a bias on the input projection (a mixer with one does not share its matrices)
 
     def _allocate(self, dtype: torch.dtype, device: torch.device) -> None:
         self.dtype = dtype
@@ -66,7 +71,7 @@ class ProjectedMixer(Mixer):
         raise NotImplementedError
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
-        rows = K.linear(x, self.in_weight)
+        rows = K.linear(x, self.in_weight, self.in_bias)
         out = torch.empty((x.shape[0], self.out_cols), dtype=rows.dtype, device=rows.device)
         self.mix_rows(rows, ctx, cache, out)
         return K.linear(out, self.o_weight)
@@ -193,7 +198,59 @@ class GatedDeltaRule(ProjectedMixer):
         K.gated_rms_norm(o, rows[:, self.channels:self.b_col], self.norm_weight, self.eps, out, scale)
 
 
+class LightningAttention(ProjectedMixer):
+    graph_safe = True
+
+    DEFAULT_TENSOR_NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "norm": "norm"}
+
+    def __init__(self, *, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, decay: tuple,
+                 eps: float, name: str, q_scale: float = 1.0, tensor_names: dict | None = None,
+                 dtype: torch.dtype, device: torch.device) -> None:
+        if min(num_heads, head_dim, value_dim) <= 0 or len(decay) != num_heads:
+            raise ValueError("lightning attention needs positive heads and sizes and one decay a head")
+        if head_dim > 512:
+            raise ValueError(f"head_dim {head_dim} exceeds the state kernel's 512 key channels")
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.head_dim, self.value_dim = int(head_dim), int(value_dim)
+        self.eps, self.name, self.q_scale = float(eps), name, float(q_scale)
+        self.tensor_names = dict(self.DEFAULT_TENSOR_NAMES)
+        self.tensor_names.update(tensor_names or {})
+        self.qk_cols, self.v_cols = self.num_heads * self.head_dim, self.num_heads * self.value_dim
+        # one packed projection: q, k, v, the gate
+        self.in_rows = _round8(2 * self.qk_cols + 2 * self.v_cols)
+        self.out_cols = self.v_cols
+        self._allocate(dtype, device)
+        self.norm_weight = torch.empty(self.v_cols, dtype=dtype, device=device)
+        table = torch.tensor([float(a) for a in decay], dtype=torch.float32)
+        self.decay = table if torch.device(device).type == "meta" else table.to(device)
+
+    def state_spec(self) -> StateSpec:
+        return StateSpec((_round4(self.num_heads * self.head_dim * self.value_dim),), torch.float32)
+
+    def _tensor(self, key: str) -> str:
+        return f"{self.name}.{self.tensor_names[key]}"
+
+    def weight_slots(self) -> list[WeightSlot]:
+        qk, v, w = self.qk_cols, self.v_cols, self.in_weight
+        return [
+            WeightSlot(self._tensor("q"), w[:qk]), WeightSlot(self._tensor("k"), w[qk:2 * qk]),
+            WeightSlot(self._tensor("v"), w[2 * qk:2 * qk + v]), WeightSlot(self._tensor("g"), w[2 * qk + v:2 * qk + 2 * v]),
+            WeightSlot(self._tensor("norm"), self.norm_weight, init="ones"),
+            WeightSlot(self._tensor("o"), self.o_weight),
+        ]
+
+    def mix_rows(self, rows, ctx, cache, out, scale: float = 1.0) -> None:
+        qk, v = self.qk_cols, self.v_cols
+        o = K.lightning_scan(rows[:, :qk], rows[:, qk:2 * qk], rows[:, 2 * qk:2 * qk + v], self.decay, cache.state, ctx,
+                             heads=self.num_heads, dim=self.head_dim, value_dim=self.value_dim, q_scale=self.q_scale,
+                             state_offset=self.state_offset)
+        # one norm over all heads' values: a single "head" as wide as the read-out
+        K.gated_rms_norm(o.view(o.shape[0], 1, v), rows[:, 2 * qk + v:2 * qk + 2 * v], self.norm_weight, self.eps,
+                         out, scale, gate_act="sigmoid")
+
+
 MIXERS.register("gated_linear_attention", GatedLinearAttention)
+MIXERS.register("lightning_attention", LightningAttention)
 MIXERS.register("gated_delta_rule", GatedDeltaRule)
 
-__all__ = ["GatedDeltaRule", "GatedLinearAttention", "ProjectedMixer"]
+__all__ = ["GatedDeltaRule", "GatedLinearAttention", "LightningAttention", "ProjectedMixer"]

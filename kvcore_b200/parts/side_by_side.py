@@ -5,7 +5,13 @@ mixers side by side on one input.
 ``rot_dims`` entries of every q and k head turn by the token's position in neighbouring pairs (entry 2i with
 entry 2i+1, frequency ``rot_base^(-2i/rot_dims) / rot_factor``); after the turn every head is divided by its
 root mean square (no weight); scores are ``q . k * scale`` over the last ``window`` positions (the token's own
-included), ordinary softmax; head ``h``'s output is multiplied by ``sigmoid(W_g x)_h``.  A token's keys and
+included), ordinary softmax; head ``h``'s output is multiplied by ``sigmoid(W_g x)_h``.  Further mechanisms, each
+a parameter: biases on q, k and v (``bias``); a sink per head that joins the softmax's denominator (``sink``); a
+bias ``slope_h * (i - j)`` taken off the score of query ``i`` and key ``j`` with
+``slope_h = 2^(-slope_exponent (h + 1) / heads)`` (``slope_exponent``); a query temperature, q times
+``1 + coef * ln(floor((position + 1) / every) + 1)`` (``q_temp = (coef, every)``); value mixing
+(``value_mix``): the ``"first"`` such layer of a model leaves its values of the step's tokens for the
+``"later"`` ones, which cache ``(1 - lambda) v + lambda v_first`` with their own number ``lambda``.  A token's keys and
 values are one cached row ``[k of all kv heads | v of all kv heads]``, so layers of any sizes share the page
 pool's machinery, and pages wholly behind the window are handed back while the request lives.
 
@@ -29,11 +35,14 @@ from .rope import rope_inverse_frequencies
 class GatedWindowAttention(ProjectedMixer):
     graph_safe = True
 
-    DEFAULT_TENSOR_NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o"}
+    DEFAULT_TENSOR_NAMES = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "q_bias": "q.b", "k_bias": "k.b",
+                            "v_bias": "v.b", "sink": "sink", "value_mix": "vmix"}
 
     def __init__(self, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
                  scale: float, window: int | None, rot_dims: int, rot_base: float, rot_factor: float = 1.0,
-                 qk_norm: bool = True, eps: float, head_gate: bool = True, name: str,
+                 qk_norm: bool = True, eps: float, head_gate: bool = True, name: str, bias: bool = False,
+                 sink: bool = False, slope_exponent: float | None = None, q_temp: tuple | None = None,
+                 value_mix: str | None = None, value_mix_key: str = "values_of_first_mixing_layer",
                  tensor_names: dict | None = None, dtype: torch.dtype, device: torch.device) -> None:
         if min(num_heads, num_kv_heads, head_dim, value_dim) <= 0 or num_heads % num_kv_heads:
             raise ValueError(f"num_heads {num_heads} must be a positive multiple of num_kv_heads {num_kv_heads}")
@@ -61,6 +70,20 @@ class GatedWindowAttention(ProjectedMixer):
         if self.rot_dims:
             table = rope_inverse_frequencies(self.rot_dims, rot_base, "linear", rot_factor)
             self.inv_freq = table if torch.device(device).type == "meta" else table.to(device)
+        if value_mix not in (None, "first", "later"):
+            raise ValueError(f"value_mix is None, 'first' or 'later', got {value_mix!r}")
+        if q_temp is not None and (len(q_temp) != 2 or int(q_temp[1]) <= 0):
+            raise ValueError(f"q_temp is (coef, every) with every > 0, got {q_temp!r}")
+        self.q_temp = None if q_temp is None else (float(q_temp[0]), int(q_temp[1]))
+        self.value_mix, self.value_mix_key = value_mix, value_mix_key
+        on_device = (lambda t: t) if torch.device(device).type == "meta" else (lambda t: t.to(device))
+        self.in_bias = torch.zeros(self.in_rows, dtype=dtype, device=device) if bias else None
+        self.sink = torch.empty(self.num_heads, dtype=torch.float32, device=device) if sink else None
+        self.lam = torch.empty((), dtype=torch.float32, device=device) if value_mix else None
+        self.slopes = None
+        if slope_exponent is not None:
+            heads = torch.arange(1, self.num_heads + 1, dtype=torch.float64)
+            self.slopes = on_device(torch.exp2(-float(slope_exponent) * heads / self.num_heads).to(torch.float32))
 
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(1, 1, self.k_cols + self.v_cols, self.window)
@@ -74,6 +97,14 @@ class GatedWindowAttention(ProjectedMixer):
                  WeightSlot(self._tensor("v"), w[q + k:self.g_col]), WeightSlot(self._tensor("o"), self.o_weight)]
         if self.has_gate:
             slots.append(WeightSlot(self._tensor("g"), w[self.g_col:self.g_col + self.num_heads]))
+        if self.in_bias is not None:
+            b = self.in_bias
+            slots += [WeightSlot(self._tensor("q_bias"), b[:q]), WeightSlot(self._tensor("k_bias"), b[q:q + k]),
+                      WeightSlot(self._tensor("v_bias"), b[q + k:self.g_col])]
+        if self.sink is not None:
+            slots.append(WeightSlot(self._tensor("sink"), self.sink, init="zeros"))
+        if self.lam is not None:      # the first mixing layer's number is a tensor of the model too, and unused
+            slots.append(WeightSlot(self._tensor("value_mix"), self.lam, init="zeros"))
         return slots
 
     def mix_rows(self, rows, ctx, cache, out, scale: float = 1.0) -> None:
@@ -81,16 +112,25 @@ class GatedWindowAttention(ProjectedMixer):
         table = ctx.block_table(cache.group)
         plane = cache.planes[0]                                # [pages, 1, page, k_cols + v_cols]
         num_pages, _, page, width = plane.shape
+        values = rows[:, self.q_cols + self.k_cols:self.g_col]
+        first = None
+        if self.value_mix == "later":
+            first = ctx.shared(self.value_mix_key, lambda: None)
+            if first is None or first.shape != values.shape:
+                raise RuntimeError(f"{self.name}: no layer in front has left values of this layer's sizes to mix in")
         K.turn_norm_kv_write(rows, self.inv_freq, self.rot_dims, ctx, table, plane, q_heads=self.num_heads,
                              k_heads=self.num_kv_heads, dim=self.head_dim, value_width=self.v_cols,
-                             norm=self.qk_norm, eps=self.eps, write=cache.owner)
+                             norm=self.qk_norm, eps=self.eps, write=cache.owner, q_temp=self.q_temp,
+                             mix_values=first, mix_weight=self.lam if first is not None else None)
+        if self.value_mix == "first":
+            ctx.shared(self.value_mix_key, lambda: values)
         q = rows[:, : self.q_cols].unflatten(1, (self.num_heads, self.head_dim))
         o = K.attention_dims(
             q, plane, plane.view(-1)[self.k_cols:], table, ctx, value_heads=self.num_kv_heads,
             group=self.num_heads // self.num_kv_heads, maps=1, key_width=self.head_dim, value_width=self.value_dim,
             page_size=page, num_pages=num_pages, key_strides=(page * width, self.head_dim, width),
             value_strides=(page * width, self.value_dim, width), scale=self.scale, window=self.window,
-            out_dtype=torch.float32)
+            sink=self.sink, slopes=self.slopes, out_dtype=torch.float32)
         gate = rows[:, self.g_col:self.g_col + self.num_heads] if self.has_gate else None
         K.head_gate(o.view(tokens, self.num_heads, self.value_dim), gate, out, scale)
 
@@ -107,7 +147,7 @@ class SideBySideMixers(Mixer):
             if not isinstance(spec, PartSpec):
                 raise ValueError("the members of side-by-side mixers are part specs")
             member = MIXERS.build(spec, dtype=dtype, device=device)
-            if not isinstance(member, ProjectedMixer):
+            if not isinstance(member, ProjectedMixer) or member.in_bias is not None:
                 raise ValueError(f"mixer kind {spec.kind!r} cannot share its projections with others")
             self.members.append(member)
         if sum(1 for m in self.members if m.cache_spec() is not None) > 1:

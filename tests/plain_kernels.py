@@ -191,7 +191,7 @@ def rms_norm_shift(x, weight, eps, out_dtype=None, *, shift=None, state=None, ct
     return y.to(out_dtype or x.dtype)
 
 
-def stream_add_norm(x, a, weight, eps, *, out=None, stack=None, depth=0, coeffs=None):
+def stream_add_norm(x, a, weight, eps, *, out=None, stack=None, depth=0, coeffs=None, rounded=None):
     result = x + _rms(a, eps) * weight.float()
     if out is None:
         out = x
@@ -202,7 +202,15 @@ def stream_add_norm(x, a, weight, eps, *, out=None, stack=None, depth=0, coeffs=
         for j in range(depth):
             avg = avg + coeffs[j].float() * stack[j]
         avg = avg + coeffs[depth].float() * result
+    if rounded is not None:
+        return out, avg, out.to(rounded)
     return out, avg
+
+
+def gelu_mul(z, rows, column):
+    zf = z.float()
+    gelu = 0.5 * zf * (1.0 + torch.tanh(0.7978845608028654 * (zf + 0.044715 * zf ** 3)))
+    return (gelu * rows[:, column:column + z.shape[1]].float()).to(z.dtype)
 
 
 def _strided(tensor, page, slot, head, strides, width):
@@ -214,7 +222,7 @@ def _strided(tensor, page, slot, head, strides, width):
 
 def attention_dims(q, keys, values, table, ctx, *, value_heads, group, maps, key_width, value_width, page_size,
                    num_pages, key_strides, value_strides, scale, sink=None, window=None, out=None, out_dtype=None,
-                   force_general=False, num_splits=None):
+                   force_general=False, num_splits=None, slopes=None):
     tokens, hq, _ = q.shape
     if out is None:
         out = torch.empty((tokens, hq, value_width), dtype=out_dtype or q.dtype, device=q.device)
@@ -237,6 +245,8 @@ def attention_dims(q, keys, values, table, ctx, *, value_heads, group, maps, key
             k = flat_k[k_begin[:, None] + torch.arange(key_width)[None]].float()
             v = flat_v[v_begin[:, None] + torch.arange(value_width)[None]].float()
             scores = (k @ q[t, h].float()) * scale
+            if slopes is not None:
+                scores = scores - slopes[h] * (pos - positions).float()
             top = scores.max() if sink is None else torch.maximum(scores.max(), sink[h])
             weights = torch.exp(scores - top)
             total = weights.sum() + (0.0 if sink is None else torch.exp(sink[h] - top))
@@ -367,20 +377,33 @@ def glu_clamped(gate_up, *, alpha, limit, shift):
     return (g * torch.sigmoid(alpha * g) * (u + shift)).to(gate_up.dtype)
 
 
-def moe_route(x, router, top, *, score="sigmoid", renormalize=False, gate_rows=None):
+def moe_route(x, router, top, *, score="sigmoid", renormalize=False, gate_rows=None, correction=None,
+              group_count=1, group_keep=1, weight_scale=1.0):
     z = x.float() @ router.float().T
     scores = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=-1)
-    ids = torch.empty(x.shape[0], top, dtype=torch.int32, device=x.device)
-    weights = torch.empty(x.shape[0], top, dtype=torch.float32, device=x.device)
-    left = scores.clone()
+    tokens, experts = scores.shape
+    ids = torch.empty(tokens, top, dtype=torch.int32, device=x.device)
+    weights = torch.empty(tokens, top, dtype=torch.float32, device=x.device)
+    left = scores.clone() if correction is None else scores + correction.float()
+    rows = torch.arange(tokens)
+    if group_keep < group_count:
+        best_of = left.reshape(tokens, group_count, experts // group_count).max(-1).values.clone()
+        kept = torch.zeros(tokens, group_count, dtype=torch.bool)
+        for _ in range(group_keep):  # the largest, the lowest index among equals
+            best = best_of.max(dim=-1, keepdim=True).values
+            index = (best_of == best).float().argmax(dim=-1)
+            kept[rows, index] = True
+            best_of[rows, index] = -float("inf")
+        left = left.masked_fill(~kept.repeat_interleave(experts // group_count, 1), -float("inf"))
     for slot in range(top):          # the largest, the lowest index among equals
         best = left.max(dim=-1, keepdim=True).values
         index = (left == best).float().argmax(dim=-1)
         ids[:, slot] = index
-        weights[:, slot] = best[:, 0]
-        left[torch.arange(x.shape[0]), index] = -float("inf")
+        weights[:, slot] = scores[rows, index]
+        left[rows, index] = -float("inf")
     if renormalize:
         weights = weights / weights.sum(-1, keepdim=True)
+    weights = weights * weight_scale
     gates = None if gate_rows is None else torch.sigmoid(x.float() @ gate_rows.float().T)
     return ids, weights, gates
 
@@ -445,7 +468,8 @@ def embed_scaled(table, ids, scale):
 
 
 def turn_norm_kv_write(rows, inv_freq, rot, ctx, table, cache, *, q_heads, k_heads, dim, value_width, norm=True,
-                       eps=0.0, q_weight=None, k_weight=None, write=True):
+                       eps=0.0, q_weight=None, k_weight=None, write=True, q_temp=None, mix_values=None,
+                       mix_weight=None):
     tokens = rows.shape[0]
     page_size = cache.shape[2]
     qc, kc = q_heads * dim, k_heads * dim
@@ -464,16 +488,23 @@ def turn_norm_kv_write(rows, inv_freq, rot, ctx, table, cache, *, q_heads, k_hea
         return x if weight is None else x * weight.float()
 
     q = prepare(rows[:, :qc].float().reshape(tokens, q_heads, dim), q_weight)
+    if q_temp is not None:
+        steps = torch.div(ctx.positions + 1, q_temp[1], rounding_mode="floor") + 1
+        q = q * (1.0 + q_temp[0] * torch.log(steps.float()))[:, None, None]
     k = prepare(rows[:, qc:qc + kc].float().reshape(tokens, k_heads, dim), k_weight).to(rows.dtype)
     rows[:, :qc] = q.to(rows.dtype).reshape(tokens, qc)
     if not write:
         return
+    values = rows[:, qc + kc:qc + kc + value_width]
+    if mix_values is not None:
+        lam = mix_weight.float()
+        values = ((1.0 - lam) * values.float() + lam * mix_values.float()).to(rows.dtype)
     for t in range(tokens):
         pos = int(ctx.positions[t])
         page = int(table[int(ctx.req_index[t]), pos // page_size])
         assert page > 0
         cache[page, 0, pos % page_size, :kc] = k[t].reshape(kc)
-        cache[page, 0, pos % page_size, kc:] = rows[t, qc + kc:qc + kc + value_width]
+        cache[page, 0, pos % page_size, kc:] = values[t]
 
 
 def head_gate(o, gate, out, scale=1.0):
@@ -551,10 +582,27 @@ def delta_scan(prepared, state, ctx, *, heads, kv_heads, dim, value_dim, state_o
     return out
 
 
-def gated_rms_norm(o, gate, weight, eps, out, scale=1.0):
+def lightning_scan(q, k, v, decay, state, ctx, *, heads, dim, value_dim, q_scale=1.0, state_offset=0):
+    tokens = q.shape[0]
+    out = torch.empty((tokens, heads, value_dim), dtype=torch.float32, device=q.device)
+    n = heads * dim * value_dim
+    silu = torch.nn.functional.silu
+    qf = silu(q.float()).reshape(tokens, heads, dim) * q_scale
+    kf, vf = silu(k.float()).reshape(tokens, heads, dim), silu(v.float()).reshape(tokens, heads, value_dim)
+    for _, begin, end, slot in _request_ranges(ctx):
+        S = state[slot, state_offset:state_offset + n].reshape(heads, value_dim, dim).transpose(1, 2).clone()   # kept column by column
+        for t in range(begin, end):
+            S = S * decay.float()[:, None, None] + kf[t][:, :, None] * vf[t][:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", S, qf[t])
+        state[slot, state_offset:state_offset + n] = S.transpose(1, 2).reshape(n)
+    return out
+
+
+def gated_rms_norm(o, gate, weight, eps, out, scale=1.0, *, gate_act="silu"):
     tokens, heads, width = o.shape
     g = gate.float().reshape(tokens, heads, width)
-    y = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight.float() * (g * torch.sigmoid(g)) * scale
+    factor = g * torch.sigmoid(g) if gate_act == "silu" else torch.sigmoid(g)
+    y = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight.float() * factor * scale
     out.copy_(y.reshape(tokens, heads * width).to(out.dtype))
     return out
 
@@ -618,7 +666,7 @@ _NAMES = [
     "rms_norm_shift", "stream_add_norm", "attention_dims", "latent_prepare", "head_norm_kv_write", "maps_combine",
     "sigmoid_gate_mul", "heads_linear", "gather_cached_rows",
     "embed_scaled", "turn_norm_kv_write", "head_gate", "gla_scan", "conv_prepare", "delta_scan", "gated_rms_norm",
-    "layer_norm", "stream_add", "qk_prepare", "glu_clamped", "moe_route", "moe_experts", "moe_combine", "moe_path",
+    "lightning_scan", "gelu_mul", "layer_norm", "stream_add", "qk_prepare", "glu_clamped", "moe_route", "moe_experts", "moe_combine", "moe_path",
 ]
 
 
