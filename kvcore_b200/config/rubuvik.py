@@ -78,7 +78,7 @@ class RubuvikConfig:
             eps=_number(_need(raw, "norm", "the model"), "eps", "norm"),
             embedding_scale=_number(_need(raw, "embedding", "the model"), "scale", "embedding"),
             residual_mult=_number(raw, "residual_mult", "the model"),
-            side_dim=_positive_int(side, "dim", "token_side") if side else 0,
+            side_dim=_positive_int(side, "dim", "token_side") if side is not None else 0,
             layers=tuple(layers),
             max_positions=int(raw.get("max_position_embeddings", DEFAULT_MAX_POSITIONS)),
             stored_dtype=raw.get("dtype") or raw.get("torch_dtype"),
@@ -183,6 +183,8 @@ class RubuvikConfig:
                 norms["feed_forward_norm"] = self._norm(f"{prefix}.norm2")
                 norms["feed_forward_out_norm"] = self._norm(f"{prefix}.norm2b", self.residual_mult)
             block = dict(hidden_size=self.width)
+            if feed_forward is None:     # a layer without a feed-forward may still carry the norms around one
+                block["unused_tensors"] = (f"{prefix}.norm2", f"{prefix}.norm2b")
             if self.side_dim:
                 block["token_side"] = dict(dim=self.side_dim, index=index, eps=self.eps, scale=self.residual_mult,
                                            name=f"{prefix}.side")

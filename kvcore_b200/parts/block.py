@@ -154,8 +154,11 @@ class SandwichResidualBlock(Block):
 
     def __init__(self, *, layer: LayerSpec, hidden_size: int, token_shift: str | None = None,
                  depth_average: str | None = None, depth: int = 0, depth_slots: int = 0,
-                 token_side: dict | None = None, dtype: torch.dtype, device: torch.device) -> None:
+                 token_side: dict | None = None, unused_tensors: tuple = (), dtype: torch.dtype,
+                 device: torch.device) -> None:
         self.hidden_size = int(hidden_size)
+        # names a checkpoint may carry for this layer although the layer has no use for them
+        self.unused_tensors = tuple(unused_tensors)
         self.dtype = dtype
         norms = layer.norms
         self.mixer_norm = NORMS.build(norms["mixer_norm"], dtype=dtype, device=device)
@@ -197,7 +200,9 @@ class SandwichResidualBlock(Block):
                                  self.feed_forward, self.feed_forward_out_norm) if p is not None)
 
     graph_safe = PreNormResidualBlock.graph_safe
-    ignorable_tensor_names = PreNormResidualBlock.ignorable_tensor_names
+
+    def ignorable_tensor_names(self) -> list[str]:
+        return PreNormResidualBlock.ignorable_tensor_names(self) + list(self.unused_tensors)
 
     def finalize_weights(self) -> None:
         PreNormResidualBlock.finalize_weights(self)

@@ -107,6 +107,10 @@ class GatedWindowAttention(ProjectedMixer):
             slots.append(WeightSlot(self._tensor("value_mix"), self.lam, init="zeros"))
         return slots
 
+    def ignorable_tensor_names(self) -> list[str]:
+        # a layer that mixes no values in may still carry the number it would mix them with
+        return [self._tensor("value_mix")] if self.lam is None else []
+
     def mix_rows(self, rows, ctx, cache, out, scale: float = 1.0) -> None:
         tokens = rows.shape[0]
         table = ctx.block_table(cache.group)

@@ -151,7 +151,7 @@ def write_safetensors(
         handle.write(blob)
         for name in ordered:
             tensor = tensors[name].detach().contiguous().cpu()
-            handle.write(tensor.view(torch.uint8).numpy().tobytes() if tensor.numel() else b"")
+            handle.write(tensor.reshape(-1).view(torch.uint8).numpy().tobytes() if tensor.numel() else b"")
 
 
 def weight_files(folder: str | Path) -> list[Path]:

@@ -119,11 +119,11 @@ def random_weights(cfg, seed, dtype=torch.float32):
         elif leaf == "sink":
             t = torch.randn(shape, generator=g)
         elif leaf == "correction":
-            t = 0.1 * torch.randn(shape, generator=g)
+            t = 0.05 * torch.randn(shape, generator=g)
         elif leaf == "b":
             t = 0.3 * torch.randn(shape, generator=g)
-        elif leaf == "router":
-            t = 2.0 * torch.randn(shape, generator=g) / math.sqrt(shape[-1])
+        elif leaf == "router":      # decisive routers: most close calls are between experts that weigh little
+            t = 4.0 * torch.randn(shape, generator=g) / math.sqrt(shape[-1])
         elif name in ("embed", "side.embed"):
             t = torch.randn(shape, generator=g)
         else:
@@ -211,9 +211,13 @@ def attention(h, m, w, p, eps, second, v_first):
     return out.reshape(T, H * V) @ w[p + "o"].T, v
 
 
+STAKE_FLOOR = 0.05      # a close call between experts that both weigh less than this is no close call
+
+
 def route(h, mlp, w, p):
-    """Chosen experts [T, top] and their weights; also the margin of every token's choice (the gap between the
-    last chosen and the first refused choice score, and between the last kept and the first refused group)."""
+    """Chosen experts [T, top] and their weights; also the margin of every token's choice: the gap between the
+    last chosen and the first refused choice score, and between the last kept and the first refused group
+    (infinite where the scores at stake are all below STAKE_FLOOR: either choice then gives nearly the same sum)."""
     r = mlp["router"]
     X, top = r["experts"], r["top"]
     s = torch.softmax(h @ w[p + "router"].T, -1)
@@ -222,14 +226,20 @@ def route(h, mlp, w, p):
     if r.get("groups"):
         count, keep = r["groups"]["count"], r["groups"]["keep"]
         best = choice.view(-1, count, X // count).max(-1).values
-        order = torch.sort(best, -1, descending=True).values
+        order = torch.sort(best, -1, descending=True)
         if keep < count:
-            margin = order[:, keep - 1] - order[:, keep]
+            weight = s.view(-1, count, X // count).max(-1).values
+            stake = torch.maximum(weight.gather(1, order.indices[:, keep - 1:keep]),
+                                  weight.gather(1, order.indices[:, keep:keep + 1]))[:, 0]
+            gap = order.values[:, keep - 1] - order.values[:, keep]
+            margin = torch.where(stake > STAKE_FLOOR, gap, margin)
         kept = torch.zeros_like(best, dtype=torch.bool).scatter(1, best.topk(keep, -1).indices, True)
         choice = choice.masked_fill(~kept.repeat_interleave(X // count, 1), -math.inf)
-    order = torch.sort(choice, -1, descending=True).values
+    order = torch.sort(choice, -1, descending=True)
     if top < X:
-        margin = torch.minimum(margin, order[:, top - 1] - order[:, top])
+        stake = torch.maximum(s.gather(1, order.indices[:, top - 1:top]), s.gather(1, order.indices[:, top:top + 1]))[:, 0]
+        gap = order.values[:, top - 1] - order.values[:, top]
+        margin = torch.minimum(margin, torch.where(stake > STAKE_FLOOR, gap, torch.full_like(gap, math.inf)))
     ids = choice.topk(top, -1).indices
     return ids, s.gather(1, ids) * r["scale"], margin
 
