@@ -669,6 +669,33 @@ def dutivik_config(size: dict, kinds: str) -> dict:
             "embedding": {"scale": 24.0}, "layers": layers}
 
 
+def rubuvik_config(size: dict, kinds: str) -> dict:
+    """A Rubuvik config.json of ``DESIGN_LAYERS`` layers.  ``kinds``: a letter per layer, "l" lightning attention
+    (half of Llama's heads, values twice as wide as the keys) with a dense feed-forward, "a" the plain window
+    attention (Llama's heads, a window of 1,024, a query temperature, value mixing) with a dense feed-forward,
+    "m" the same with a mixture of experts (four groups of which two are kept), "b" the attention with biases,
+    unit q and k, a sink and a gate a head.  Every layer adds a token side input of 256 entries."""
+    half, dim = size["heads"] // 2, size["dim"]
+    dense = {"kind": "dense", "ff": size["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": size["expert_ff"]}, "shared": {"ff": size["shared_ff"]},
+           "router": {"experts": size["experts"], "top": size["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    layers = []
+    for kind in (kinds * DESIGN_LAYERS)[:DESIGN_LAYERS]:
+        if kind == "l":
+            decay = [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, half - 1)) for h in range(half)]
+            layers.append({"type": "lightning", "mlp": dense,
+                           "mixer": {"heads": half, "dim": dim, "vdim": 2 * dim, "decay": decay}})
+            continue
+        mixer = {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                 "mask": {"size": 1024}, "v_mix": True}
+        if kind != "b":
+            mixer["q_temp"] = {"coef": 0.1, "every": 1024}
+        layers.append({"type": "attention_2" if kind == "b" else "attention", "mixer": mixer,
+                       "mlp": moe if kind == "m" else dense})
+    return {"architecture": "Rubuvik", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 24.0}, "residual_mult": 0.6, "token_side": {"dim": 256}, "layers": layers}
+
+
 def llama_config(size: dict) -> dict:
     return dict(LLAMA_31_8B, hidden_size=size["width"], intermediate_size=size["ff"], num_hidden_layers=DESIGN_LAYERS,
                 num_attention_heads=size["heads"], num_key_value_heads=size["kv_heads"], head_dim=size["dim"],
@@ -719,6 +746,14 @@ def compare_designs(args) -> int:
                 "toposun_dense_full_window": toposun_config(size, "dense", 1 << 20, 0),
                 "toposun_dense": toposun_config(size, "dense", 1024, 4),
                 "toposun_moe": toposun_config(size, "moe", 1024, 4),
+            })
+        elif args.designs_of == "rubuvik":
+            models.update({
+                "dutivik_mixed": dutivik_config(size, "gppp"),
+                "rubuvik_lightning": rubuvik_config(size, "l"),
+                "rubuvik_attention": rubuvik_config(size, "ab"),
+                "rubuvik_moe": rubuvik_config(size, "m"),
+                "rubuvik_mixed": rubuvik_config(size, "lmbl"),
             })
         elif args.designs_of == "dutivik":
             models.update({
@@ -800,7 +835,7 @@ def main() -> int:
     parser.add_argument("--designs", action="store_true",
                         help="instead: Toposun (dense and mixture feed-forward) beside a Llama of equal layer sizes, "
                              "prefill and decode throughput and each kernel's share of a step; prints a line of its own")
-    parser.add_argument("--designs-of", default="toposun", choices=["toposun", "pipesun", "dutivik"],
+    parser.add_argument("--designs-of", default="toposun", choices=["toposun", "pipesun", "dutivik", "rubuvik"],
                         help="which design --designs sets beside Llama")
     parser.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="one size of --designs")
     args = parser.parse_args()

@@ -695,12 +695,48 @@ gated_rms_norm_kernel(T* __restrict__ out, long long out_stride, const float* __
   }
 }
 
+// The same for vectors of more than a thousand entries (one norm over all heads of a token): a block a vector.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_rms_norm_wide_kernel(T* __restrict__ out, long long out_stride, const float* __restrict__ o,
+                           const T* __restrict__ gate, long long gate_stride, const T* __restrict__ weight, int heads,
+                           int V, float eps, float scale, int sigmoid_gate) {
+  KVB_KERNEL_PROLOGUE(KVB_TAG_GATED_NORM);
+  __shared__ float scratch[32];
+  const long long n = blockIdx.x;
+  const long long t = n / heads;
+  const int h = (int)(n % heads);
+  const float* src = o + n * V;
+  const T* g = gate + t * gate_stride + (long long)h * V;
+  T* dst = out + t * out_stride + (long long)h * V;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < V; i += 256) { const float v = src[i]; ss = fmaf(v, v, ss); }
+  const float inv = scale / sqrtf(block_sum(ss, scratch) / (float)V + eps);
+  for (int i = threadIdx.x; i < V; i += 256) {
+    const float gv = to_float(g[i]);
+    const float sig = 1.0f / (1.0f + expf(-gv));
+    dst[i] = from_float<T>(src[i] * inv * to_float(weight[i]) * (sigmoid_gate ? sig : gv * sig));
+  }
+}
+
 extern "C" int kvb_gated_rms_norm(void* out, long long out_stride, const float* o, const void* gate,
                                   long long gate_stride, const void* weight, int tokens, int heads, int V, float eps,
                                   float scale, int sigmoid_gate, int dtype, cudaStream_t stream) {
   const long long vectors = (long long)tokens * heads;
   if (vectors == 0) return 0;
   KVB_REQUIRE(V > 0, "gated_rms_norm: bad width");
+  if (V > 1024 && vectors <= 0x7fffffffLL) {
+    if (dtype == KVB_F32)
+      KVB_CHECK_CUDA(kvb_launch((gated_rms_norm_wide_kernel<float>), dim3((unsigned)vectors), dim3(256), 0, stream, true,
+          (float*)out, out_stride, o, (const float*)gate, gate_stride, (const float*)weight, heads, V, eps, scale,
+          sigmoid_gate));
+    else
+      KVB_CHECK_CUDA(kvb_launch((gated_rms_norm_wide_kernel<bf16>), dim3((unsigned)vectors), dim3(256), 0, stream, true,
+          (bf16*)out, out_stride, o, (const bf16*)gate, gate_stride, (const bf16*)weight, heads, V, eps, scale,
+          sigmoid_gate));
+    KVB_CHECK_LAUNCH();
+    return 0;
+  }
   const long long wanted = (vectors + CP_THREADS / 32 - 1) / (CP_THREADS / 32);
   const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
   const int blocks = (int)(wanted < resident ? wanted : resident);

@@ -1810,15 +1810,17 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, gate_
             hidden = silu_mul(both.view(experts * stride, two_ff), 0).view(experts, stride, ff)
             out = torch.bmm(hidden, down.transpose(1, 2)).view(experts * stride, n)
         else:
+            # an expert's rows rounded up to 64 as well (the rows beyond its pairs are zeros): few shapes again
+            counts = [min(stride, -(-(begins[e + 1] - begins[e]) // 64) * 64) for e in range(experts)]
             both = torch.zeros((experts, stride, two_ff), dtype=x.dtype, device=x.device)
             for e in range(experts):
-                if begins[e + 1] > begins[e]:
-                    torch.mm(gathered[e, : begins[e + 1] - begins[e]], gate_up[e].t(), out=both[e, : begins[e + 1] - begins[e]])
+                if counts[e]:
+                    torch.mm(gathered[e, : counts[e]], gate_up[e].t(), out=both[e, : counts[e]])
             hidden = silu_mul(both.view(experts * stride, two_ff), 0).view(experts, stride, ff)
             out = torch.empty((experts, stride, n), dtype=x.dtype, device=x.device)
             for e in range(experts):
-                if begins[e + 1] > begins[e]:
-                    torch.mm(hidden[e, : begins[e + 1] - begins[e]], down[e].t(), out=out[e, : begins[e + 1] - begins[e]])
+                if counts[e]:
+                    torch.mm(hidden[e, : counts[e]], down[e].t(), out=out[e, : counts[e]])
             out = out.view(experts * stride, n)
         return ExpertRows(out, row_of_pair, None if weight_on_input else weights.reshape(-1))
     hidden = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
