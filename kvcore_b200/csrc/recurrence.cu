@@ -12,8 +12,8 @@
 //         with q_t, k_t, v_t, beta_t, g_t as `conv_prepare` left them (32-bit).
 //     one fixed decay a head (lightning attention):
 //         S <- a_h S + k_t v_t^T,                       o_t = S^T q_t
-//         with q_t = silu(.) * q_scale and k_t = silu(.) as `lightning_prepare` left them (32-bit), v_t passed
-//         through SiLU on its way into shared memory, a_h a constant of the model;
+//         with q_t = silu(.) * q_scale, k_t = silu(.) and v_t = silu(.) as `lightning_prepare` left them (32-bit),
+//         a_h a constant of the model;
 //   S is kept column by column ([H, V, D] in the state row: a column's D rows lie together).  A column is shared
 //   by RSPLIT neighbouring lanes (4, 8 or 16 rows each, in registers, loaded and stored as 16-byte pieces); a
 //   thread holds those rows of one column or of four neighbouring ones; a block owns 128 / RSPLIT (times four)
@@ -55,7 +55,6 @@ struct ScanParams {
   int vec16;                                // every vector starts on a 16-byte boundary and D is a multiple of 4
   int state16;                              // so does every column of S in the state rows
   const void* v; long long v_token;         // values [V] of head h at v + t * v_token + h * V (elements)
-  int v_silu;                               // the values pass SiLU (in 32-bit) on their way in
   const float* beta; const float* gate;     // [T, H] with row stride bg_stride (delta rule)
   long long bg_stride;
   float* out;                               // [T, H, V]
@@ -177,11 +176,7 @@ state_scan_kernel(ScanParams p) {
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int e = tid + j * SCAN_THREADS, tt = e / COLS, cc = blockIdx.z * COLS + e % COLS;
-      if (e < BATCH * COLS) {
-        float x = (tt < nb && cc < V) ? to_float(held[j]) : 0.0f;
-        if (MODE == 2 && p.v_silu) x = x / (1.0f + expf(-x));
-        values[stage * BATCH * COLS + e] = x;
-      }
+      if (e < BATCH * COLS) values[stage * BATCH * COLS + e] = (tt < nb && cc < V) ? to_float(held[j]) : 0.0f;
     }
   };
   const float head_decay = MODE == 2 ? p.a[h] : 0.0f;
@@ -483,25 +478,42 @@ extern "C" int kvb_gla_scan(float* out, float* prepared, const void* q, const vo
                           : launch_state_scan<bf16, 0>(p, num_reqs, tokens, stream);
 }
 
-// What the fixed-decay scan reads, 32-bit [T, 2 * H * D]: silu(q) times q_scale, silu(k).
+// What the fixed-decay scan reads, 32-bit [T, 2 * H * D + H * V]: silu(q) times q_scale, silu(k), silu(v).
+// QUADS: four neighbouring entries a thread, loaded and stored as one piece (widths that are multiples of four,
+// rows and pointers on the boundaries of such pieces).
 template <typename T>
+struct __align__(4 * sizeof(T)) ScanQuad { T v[4]; };
+
+__device__ __forceinline__ float scan_silu(float x) { return __fdividef(x, 1.0f + expf(-x)); }
+
+template <typename T, bool QUADS>
 __global__ void __launch_bounds__(256)
 lightning_prepare_kernel(float* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k,
-                         long long row_stride, long long tokens, int width, float q_scale) {
+                         const T* __restrict__ v, long long row_stride, long long tokens, int width, int vwidth,
+                         float q_scale) {
   KVB_KERNEL_PROLOGUE(KVB_TAG_LIGHTNING_PREPARE);
-  const long long total = tokens * width;
+  constexpr int N = QUADS ? 4 : 1;
+  const int per_token = (2 * width + vwidth) / N;
+  const long long total = tokens * per_token;
   for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
-    const long long t = e / width;
-    const int i = (int)(e - t * width);
-    float* row = out + t * 2 * width;
-    const float qv = to_float(q[t * row_stride + i]), kv = to_float(k[t * row_stride + i]);
-    row[i] = qv / (1.0f + expf(-qv)) * q_scale;
-    row[width + i] = kv / (1.0f + expf(-kv));
+    const long long t = e / per_token;
+    const int i = (int)(e - t * per_token) * N;
+    const T* src = (i < width ? q + i : i < 2 * width ? k + (i - width) : v + (i - 2 * width)) + t * row_stride;
+    const float factor = i < width ? q_scale : 1.0f;
+    if (QUADS) {
+      const ScanQuad<T> in = *reinterpret_cast<const ScanQuad<T>*>(src);
+      ScanQuad<float> y;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) y.v[j] = scan_silu(to_float(in.v[j])) * factor;
+      *reinterpret_cast<ScanQuad<float>*>(out + e * 4) = y;
+    } else {
+      out[e] = scan_silu(to_float(src[0])) * factor;
+    }
   }
 }
 
 // One fixed decay a head.  q, k, v: columns of the projected rows (row stride `row_stride`, heads side by side),
-// all three passed through SiLU; decay [H] 32-bit; prepared: scratch, 32-bit [T, 2 * H * D].
+// all three passed through SiLU; decay [H] 32-bit; prepared: scratch, 32-bit [T, 2 * H * D + H * V].
 extern "C" int kvb_lightning_scan(float* out, float* prepared, const void* q, const void* k, const void* v,
                                   long long row_stride, const float* decay, float* state, long long state_stride,
                                   long long state_offset, const int* query_start, const int* state_slots, int tokens,
@@ -510,24 +522,27 @@ extern "C" int kvb_lightning_scan(float* out, float* prepared, const void* q, co
   if (num_reqs == 0 || tokens == 0) return 0;
   KVB_REQUIRE(heads > 0 && D > 0 && V > 0 && decay != nullptr, "lightning_scan: bad sizes");
   KVB_REQUIRE(heads <= 65535, "lightning_scan: too many heads");
-  const int width = heads * D;
-  const long long wanted = ((long long)tokens * width + 255) / 256;
+  const int width = heads * D, vwidth = heads * V;
+  const long long per_token = 2LL * width + vwidth;
+  const size_t piece = 4 * (dtype == KVB_F32 ? sizeof(float) : sizeof(bf16));
+  const bool quads = width % 4 == 0 && vwidth % 4 == 0 && row_stride % 4 == 0 && aligned16(prepared) &&
+                     ((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % piece == 0;
+  const long long wanted = ((long long)tokens * per_token / (quads ? 4 : 1) + 255) / 256;
   const long long resident = (long long)(kvb_sm_count() > 0 ? kvb_sm_count() : 1) * 16;
   const dim3 grid((unsigned)(wanted < resident ? wanted : resident));
-  if (dtype == KVB_F32)
-    KVB_CHECK_CUDA(kvb_launch((lightning_prepare_kernel<float>), grid, dim3(256), 0, stream, true, prepared,
-        (const float*)q, (const float*)k, row_stride, (long long)tokens, width, q_scale));
-  else
-    KVB_CHECK_CUDA(kvb_launch((lightning_prepare_kernel<bf16>), grid, dim3(256), 0, stream, true, prepared,
-        (const bf16*)q, (const bf16*)k, row_stride, (long long)tokens, width, q_scale));
+#define KVB_LP_LAUNCH(T_, Q_)                                                                                  \
+  KVB_CHECK_CUDA(kvb_launch((lightning_prepare_kernel<T_, Q_>), grid, dim3(256), 0, stream, true, prepared,    \
+      (const T_*)q, (const T_*)k, (const T_*)v, row_stride, (long long)tokens, width, vwidth, q_scale))
+  if (dtype == KVB_F32) { if (quads) KVB_LP_LAUNCH(float, true); else KVB_LP_LAUNCH(float, false); }
+  else { if (quads) KVB_LP_LAUNCH(bf16, true); else KVB_LP_LAUNCH(bf16, false); }
+#undef KVB_LP_LAUNCH
   ScanParams p = {};
-  p.q = prepared; p.k = prepared + width; p.a = decay; p.vec_token = 2LL * width;
-  p.v = v; p.v_token = row_stride; p.v_silu = 1;
+  p.q = prepared; p.k = prepared + width; p.a = decay; p.vec_token = per_token;
+  p.v = prepared + 2 * width; p.v_token = per_token;
   p.out = out; p.state = state; p.state_stride = state_stride; p.state_offset = state_offset;
   p.query_start = query_start; p.state_slots = state_slots;
   p.heads = heads; p.kv_share = 1; p.D = D; p.V = V;
-  return dtype == KVB_F32 ? launch_state_scan<float, 2>(p, num_reqs, tokens, stream)
-                          : launch_state_scan<bf16, 2>(p, num_reqs, tokens, stream);
+  return launch_state_scan<float, 2>(p, num_reqs, tokens, stream);
 }
 
 // Delta rule.  prepared [T, 2 * G * D + H * V + 2 * H] 32-bit as conv_prepare leaves it: q, k (G heads), v, beta, gate.
@@ -697,7 +712,7 @@ gated_rms_norm_kernel(T* __restrict__ out, long long out_stride, const float* __
 
 // The same for vectors of more than a thousand entries (one norm over all heads of a token): a block a vector.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 gated_rms_norm_wide_kernel(T* __restrict__ out, long long out_stride, const float* __restrict__ o,
                            const T* __restrict__ gate, long long gate_stride, const T* __restrict__ weight, int heads,
                            int V, float eps, float scale, int sigmoid_gate) {
@@ -710,9 +725,9 @@ gated_rms_norm_wide_kernel(T* __restrict__ out, long long out_stride, const floa
   const T* g = gate + t * gate_stride + (long long)h * V;
   T* dst = out + t * out_stride + (long long)h * V;
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < V; i += 256) { const float v = src[i]; ss = fmaf(v, v, ss); }
+  for (int i = threadIdx.x; i < V; i += blockDim.x) { const float v = src[i]; ss = fmaf(v, v, ss); }
   const float inv = scale / sqrtf(block_sum(ss, scratch) / (float)V + eps);
-  for (int i = threadIdx.x; i < V; i += 256) {
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
     const float gv = to_float(g[i]);
     const float sig = 1.0f / (1.0f + expf(-gv));
     dst[i] = from_float<T>(src[i] * inv * to_float(weight[i]) * (sigmoid_gate ? sig : gv * sig));
@@ -726,12 +741,14 @@ extern "C" int kvb_gated_rms_norm(void* out, long long out_stride, const float* 
   if (vectors == 0) return 0;
   KVB_REQUIRE(V > 0, "gated_rms_norm: bad width");
   if (V > 1024 && vectors <= 0x7fffffffLL) {
+    // the threads of a block follow the width alone, so a vector's sum does not depend on the batch
+    const int wide_threads = V >= 4096 ? 1024 : V >= 2048 ? 512 : 256;
     if (dtype == KVB_F32)
-      KVB_CHECK_CUDA(kvb_launch((gated_rms_norm_wide_kernel<float>), dim3((unsigned)vectors), dim3(256), 0, stream, true,
+      KVB_CHECK_CUDA(kvb_launch((gated_rms_norm_wide_kernel<float>), dim3((unsigned)vectors), dim3(wide_threads), 0, stream, true,
           (float*)out, out_stride, o, (const float*)gate, gate_stride, (const float*)weight, heads, V, eps, scale,
           sigmoid_gate));
     else
-      KVB_CHECK_CUDA(kvb_launch((gated_rms_norm_wide_kernel<bf16>), dim3((unsigned)vectors), dim3(256), 0, stream, true,
+      KVB_CHECK_CUDA(kvb_launch((gated_rms_norm_wide_kernel<bf16>), dim3((unsigned)vectors), dim3(wide_threads), 0, stream, true,
           (bf16*)out, out_stride, o, (const bf16*)gate, gate_stride, (const bf16*)weight, heads, V, eps, scale,
           sigmoid_gate));
     KVB_CHECK_LAUNCH();

@@ -1532,8 +1532,8 @@ def lightning_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
         raise KernelError(f"lightning_scan: {decay.numel()} decays for {heads} heads")
     _state_row(state, state_offset, heads * dim * value_dim)
     out = torch.empty((q.shape[0], heads, value_dim), dtype=torch.float32, device=q.device)
-    # what the scan reads a token, 32-bit: silu(q) times its scale, silu(k)
-    prepared = torch.empty((q.shape[0], 2 * heads * dim), dtype=torch.float32, device=q.device)
+    # what the scan reads a token, 32-bit: silu(q) times its scale, silu(k), silu(v)
+    prepared = torch.empty((q.shape[0], 2 * heads * dim + heads * value_dim), dtype=torch.float32, device=q.device)
     _call("kvb_lightning_scan", out.data_ptr(), prepared.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
           q.stride(0), decay.data_ptr(), state.data_ptr(), state.stride(0), state_offset, ctx.query_start.data_ptr(),
           ctx.state_slots.data_ptr(), q.shape[0], ctx.num_reqs, heads, dim, value_dim, float(q_scale),
