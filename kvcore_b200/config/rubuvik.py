@@ -94,8 +94,8 @@ class RubuvikConfig:
         heads = _positive_int(m, "heads", where)
         decay = _need(m, "decay", where)
         if (not isinstance(decay, (list, tuple)) or len(decay) != heads
-                or any(isinstance(a, bool) or not isinstance(a, (int, float)) or not 0.0 <= a <= 1.0 for a in decay)):
-            raise ConfigError(f"config.json: {where}.decay must be {heads} numbers in [0, 1], one a head")
+                or any(isinstance(a, bool) or not isinstance(a, (int, float)) or not 0.0 <= a < float("inf") for a in decay)):
+            raise ConfigError(f"config.json: {where}.decay must be {heads} numbers that are not negative, one a head")
         return PartSpec("lightning_attention", dict(
             hidden_size=self.width, num_heads=heads, head_dim=_positive_int(m, "dim", where),
             value_dim=_positive_int(m, "vdim", where), decay=tuple(float(a) for a in decay), eps=self.eps,

@@ -182,7 +182,7 @@ def test_config_gives_every_constant_to_the_parts():
     (lambda c: c["layers"][0]["mlp"].update(kind="glu"), "feed-forward of this design"),
     (lambda c: c["layers"][0]["mixer"].update(heads=3), "multiple"),
     (lambda c: c["layers"][1]["mixer"].update(decay=[0.5]), "one a head"),
-    (lambda c: c["layers"][1]["mixer"].update(decay=[0.5, 1.5]), "one a head"),
+    (lambda c: c["layers"][1]["mixer"].update(decay=[0.5, -0.5]), "one a head"),
     (lambda c: c["layers"][1]["mlp"]["router"].update(top=9), "exceeds experts"),
     (lambda c: c["layers"][1]["mlp"]["router"]["groups"].update(count=3), "equal groups"),
     (lambda c: c["layers"][1]["mlp"]["router"]["groups"].update(keep=1), "must hold"),
