@@ -379,6 +379,79 @@ def test_each_mechanism_changes_the_logits():
     assert moved(changed(lambda c: c["layers"][1]["mlp"].pop("shared"))) > 1e-3
 
 
+# ---- configurations drawn at random ------------------------------------------------------------------------
+def drawn_config(seed):
+    """Another model of the design: sizes, head counts, order of layers, windows and constants all drawn."""
+    import random
+
+    rng = random.Random(seed)
+    fast = seed % 2 == 0                       # every other model has widths the tensor-core attention takes
+    width = rng.choice([32, 48, 64, 96] if fast else [24, 40, 56, 72])
+    mixing_kv, mixing_vdim = rng.choice([1, 2, 3]), rng.choice([8, 16, 24, 40] if fast else [6, 10, 12, 20])
+    layers = []
+    for _ in range(rng.randrange(2, 6)):
+        kind = rng.choice(["lightning", "attention", "attention_2"])
+        mlp = rng.choice([None, "dense", "moe", "moe"])
+        if mlp == "dense":
+            mlp = P.dense(rng.choice([16, 24, 40, 52]))
+        elif mlp == "moe":
+            count = rng.choice([1, 2, 3, 4])
+            per = rng.choice([1, 2, 3])
+            keep = rng.randrange(1, count + 1)
+            top = rng.randrange(1, keep * per + 1)
+            mlp = P.moe(experts=count * per, top=top, ff=rng.choice([8, 12, 16, 20]),
+                        groups=None if count == 1 and rng.random() < 0.5 else (count, keep), scale=rng.choice([1.0, 0.5, 2.5]),
+                        shared=rng.choice([None, 16, 24]))
+        if kind == "lightning":
+            heads = rng.choice([1, 2, 3, 4])
+            layers.append(L(heads=heads, dim=rng.choice([16, 32, 64] if fast else [4, 6, 10, 24]),
+                            vdim=rng.choice([8, 16, 32, 40] if fast else [5, 6, 12, 20]),
+                            decay=[rng.choice([0.0, 0.3, 0.8, 0.95, 0.999, 1.0]) for _ in range(heads)], mlp=mlp))
+            continue
+        mixes = rng.random() < 0.7
+        kv_heads = mixing_kv if mixes else rng.choice([1, 2])
+        layers.append(A(kind=kind, heads=kv_heads * rng.choice([1, 2, 3]), kv_heads=kv_heads,
+                        dim=rng.choice([16, 32, 48, 64] if fast else [6, 10, 20, 28]),
+                        vdim=mixing_vdim if mixes else rng.choice([8, 24] if fast else [7, 9]),
+                        window=rng.choice([None, 1, 2, 5, 16, 17, 31, 40, 64]), scale=rng.choice([None, 0.2, 0.05]),
+                        q_temp=rng.choice([None, (0.5, 1), (0.25, 7), (1.0, 16), (0.1, 300)]), v_mix=mixes, mlp=mlp))
+    return P.model_config(layers, vocab=rng.randrange(40, 160), width=width, eps=rng.choice([1e-6, 1e-5]),
+                          embedding_scale=rng.choice([1.0, 0.5, 3.0]), residual_mult=rng.choice([1.0, 0.7, 0.4]),
+                          side=rng.choice([None, 4, 6, 8, 16]))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, device, tmp_path):
+    """Eight other models of the design through the framework: in 32-bit every position of every cutting against
+    the plain statement (and, on the GPU, bit-equal between cuttings); in bfloat16 the mixed cutting."""
+    cfg = drawn_config(seed)
+    folder = tmp_path / "m"
+    weights = write_folder(folder, cfg, seed=100 + seed)
+    requests = {f"d{i}": rc.random_tokens(cfg["vocab"], n, 500 + 10 * seed + i) for i, n in enumerate((1, 2, 47, 90, 33))}
+    reference, margins = {}, {}
+    for rid, toks in requests.items():
+        seen = []
+        reference[rid] = P.forward(cfg, weights, toks, margins=seen).numpy()
+        margins[rid] = seen[0].numpy()
+    traces = {"whole": rc.trace_whole(requests), "tail": rc.trace_decode_tail(requests, tail=40),
+              "chunks": rc.trace_chunks(requests, sizes=(2, 13, 1, 5, 32, 3)),
+              "mixed": rc.trace_mixed(requests, max_live=3, seed=seed)}
+    results = {}
+    for name, steps in traces.items():
+        out = tmp_path / name
+        rc.run_inprocess(folder, "float32", steps, out, rc.peak_tokens(steps), device=device,
+                         fill_freed_pages="poison" if name == "mixed" else None)
+        results[name] = rc.collect(steps, out, cfg["vocab"])
+        compare(results[name], reference, "float32")
+    if device != "cpu":
+        for name in ("tail", "chunks", "mixed"):
+            for key, row in results["whole"].items():
+                assert np.array_equal(row, results[name][key]), f"{name} differs from whole at {key}"
+    steps = traces["mixed"]
+    rc.run_inprocess(folder, "bfloat16", steps, tmp_path / "b", rc.peak_tokens(steps), device=device, fill_freed_pages="poison")
+    compare(rc.collect(steps, tmp_path / "b", cfg["vocab"]), reference, "bfloat16", margins)
+
+
 # ---- the entry point and the scheduler -------------------------------------------------------------------
 def plain_greedy(cfg, weights, prompt, steps):
     tokens = list(prompt)
