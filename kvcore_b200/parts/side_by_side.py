@@ -129,12 +129,17 @@ class GatedWindowAttention(ProjectedMixer):
         if self.value_mix == "first":
             ctx.shared(self.value_mix_key, lambda: values)
         q = rows[:, : self.q_cols].unflatten(1, (self.num_heads, self.head_dim))
+        # without a gate and without a scale the attention writes the rows of the output product itself
+        direct = not self.has_gate and scale == 1.0
         o = K.attention_dims(
             q, plane, plane.view(-1)[self.k_cols:], table, ctx, value_heads=self.num_kv_heads,
             group=self.num_heads // self.num_kv_heads, maps=1, key_width=self.head_dim, value_width=self.value_dim,
             page_size=page, num_pages=num_pages, key_strides=(page * width, self.head_dim, width),
             value_strides=(page * width, self.value_dim, width), scale=self.scale, window=self.window,
-            sink=self.sink, slopes=self.slopes, out_dtype=torch.float32)
+            sink=self.sink, slopes=self.slopes, out_dtype=torch.float32,
+            out=out.unflatten(1, (self.num_heads, self.value_dim)) if direct else None)
+        if direct:
+            return
         gate = rows[:, self.g_col:self.g_col + self.num_heads] if self.has_gate else None
         K.head_gate(o.view(tokens, self.num_heads, self.value_dim), gate, out, scale)
 
