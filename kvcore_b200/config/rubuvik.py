@@ -156,7 +156,7 @@ class RubuvikConfig:
     def to_model_spec(self) -> ModelSpec:
         layers = []
         count = len(self.layers)
-        first_mix: dict[str, Any] | None = None      # sizes of the first layer that mixes values
+        first_mix: int | None = None      # width of a token's values in the first layer that mixes values
         for index, layer in enumerate(self.layers):
             kind = _need(layer, "type", f"layers[{index}]")
             m = _need(layer, "mixer", f"layers[{index}]")
@@ -165,7 +165,8 @@ class RubuvikConfig:
             elif kind in ("attention", "attention_2"):
                 mixes = None
                 if m.get("v_mix"):
-                    sizes = {key: m.get(key) for key in ("kv_heads", "vdim")}
+                    # the values are mixed entry by entry: what must agree is the width of a token's values
+                    sizes = _positive_int(m, "kv_heads", f"layers[{index}].mixer") * _positive_int(m, "vdim", f"layers[{index}].mixer")
                     if first_mix is None:
                         first_mix, mixes = sizes, "first"
                     elif sizes != first_mix:

@@ -179,6 +179,10 @@ def attention(h, m, w, p, eps, second, v_first):
     q, k, v = h @ w[p + "q"].T, h @ w[p + "k"].T, h @ w[p + "v"].T
     if second:
         q, k, v = q + w[p + "q.b"], k + w[p + "k.b"], v + w[p + "v.b"]
+    if m.get("v_mix") and v_first is not None:          # entry by entry over all key/value heads together
+        lam = w[p + "vmix"]
+        v = (1.0 - lam) * v + lam * v_first
+    cached = v
     q, k, v = q.view(T, H, D), k.view(T, G, D), v.view(T, G, V)
     if second:
         q, k = unit_rms(q, eps), unit_rms(k, eps)
@@ -186,9 +190,6 @@ def attention(h, m, w, p, eps, second, v_first):
     if m.get("q_temp"):
         steps = torch.floor((position + 1) / m["q_temp"]["every"]) + 1.0
         q = q * (1.0 + m["q_temp"]["coef"] * torch.log(steps)).to(h.dtype)[:, None, None]
-    if m.get("v_mix") and v_first is not None:
-        lam = w[p + "vmix"]
-        v = (1.0 - lam) * v + lam * v_first
     distance = position[:, None] - position[None, :]                    # i - j
     seen = distance >= 0
     if m.get("mask"):
@@ -208,7 +209,7 @@ def attention(h, m, w, p, eps, second, v_first):
         out[:, head] = weights @ v[:, kv]
     if second:
         out = out * torch.sigmoid(h @ w[p + "g"].T)[:, :, None]
-    return out.reshape(T, H * V) @ w[p + "o"].T, v
+    return out.reshape(T, H * V) @ w[p + "o"].T, cached
 
 
 STAKE_FLOOR = 0.05      # a close call between experts that both weigh less than this is no close call

@@ -67,6 +67,7 @@ CONFIGS = {
         A(heads=1, kv_heads=1, dim=20, vdim=6, window=500, mlp=P.moe(experts=3, top=1, ff=10)),
         L(heads=3, dim=10, vdim=6, decay=(0.0, 0.5, 0.97), mlp=None),
         A(kind="attention_2", heads=3, kv_heads=1, dim=6, vdim=10, v_mix=True, mlp=P.dense(20)),
+        A(heads=2, kv_heads=2, dim=8, vdim=5, v_mix=True, mlp=None),      # the same width of values, cut into other heads
     ], vocab=61, width=40, eps=1e-6),
     # sizes the tensor-core attention takes (widths in steps of 16), windows across several pages, key sizes that
     # fill the state kernel's registers and ones that are shared by two threads a column
